@@ -1,0 +1,132 @@
+/*
+ * kiln_w4a16.h -- C ABI of the B200 (sm_100a) W4A16 quantised-linear library.
+ *
+ * Drop-in boundary for kiln's `kiln-marlin-gemm` crate: packed symmetric int4
+ * weights (Marlin tile/fragment layout, group 128 along K or per-column) +
+ * fp16 scales + bf16 activations -> bf16 output, fp32 accumulation.
+ * All pointers are plain device (or, where stated, host) pointers; every
+ * matrix is row-major and contiguous.  No entry point synchronises the stream
+ * unless it says so.  Paths in the comments are relative to the kiln tree.
+ */
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int kiln_w4a16_status_t;
+
+/* 0..2 keep the reference's meaning (crates/kiln-marlin-gemm/csrc/marlin_kernel.cu:728-729,
+ * crates/kiln-marlin-gemm/csrc/marlin_kernel.h:35-38). */
+#define KILN_W4A16_OK 0
+#define KILN_W4A16_ERR_PROB_SHAPE 1 /* k % 128, n % 256 (n % 64 for a shard), bad groupsize */
+#define KILN_W4A16_ERR_KERN_SHAPE 2 /* no kernel configuration for the request */
+#define KILN_W4A16_ERR_ALIGNMENT 3  /* a pointer is not 16-byte aligned */
+#define KILN_W4A16_ERR_WORKSPACE 4  /* workspace missing or too small */
+#define KILN_W4A16_ERR_CUDA 5       /* a CUDA runtime/driver call failed (see kiln_w4a16_last_cuda_error) */
+#define KILN_W4A16_ERR_TIMEOUT 6    /* a bounded device-side wait gave up (read from the status word) */
+#define KILN_W4A16_ERR_ARG 7        /* null pointer / negative size / size above a stated maximum */
+
+/* Replaces kiln_marlin_w4a16_gemm (crates/kiln-marlin-gemm/csrc/marlin_kernel.h:39-55,
+ * crates/kiln-marlin-gemm/csrc/marlin_kernel.cu:831-860; Rust declaration
+ * crates/kiln-marlin-gemm/src/lib.rs:50-68).  Same symbol, same argument order.
+ * Differences, all removing work from the caller:
+ *   - A [prob_m, prob_k] and C [prob_m, prob_n] are bf16 (the reference kernel is
+ *     fp16-only and its wrapper casts on both sides, lib.rs:169, 269);
+ *   - `workspace` is scratch for split-K partial sums; it must hold at least
+ *     kiln_w4a16_workspace_bytes(prob_m, prob_n, prob_k) bytes.  It needs no
+ *     zero-initialisation and its contents after the call are unspecified.
+ *     NULL is accepted when that function returns 0;
+ *   - `dev` is ignored: the launch goes to the device that owns `stream`'s context
+ *     (the reference hard-codes ordinal 0, lib.rs:210-215);
+ *   - thread_k / thread_n / sms / max_par are accepted for signature compatibility;
+ *     only -1 ("auto", what the reference wrapper always passes, lib.rs:252-255)
+ *     or the reference's own legal values are accepted, and they do not select a tile.
+ * B is int32 [prob_k/16, 2*prob_n] in the Marlin layout, s is fp16
+ * [prob_k/groupsize, prob_n] (one row for groupsize -1) in the Marlin scale order.
+ * Stream-ordered, asynchronous, capturable in a CUDA graph after one warm-up call
+ * per device (function attributes and tensor maps are created on first use). */
+kiln_w4a16_status_t kiln_marlin_w4a16_gemm(const void *A, const void *B, void *C, void *s, int prob_m,
+                                           int prob_n, int prob_k, void *workspace, int groupsize,
+                                           int dev, void *stream, int thread_k, int thread_n, int sms,
+                                           int max_par);
+
+/* Same operation with an explicit workspace size (checked) and without the
+ * reference's unused tuning arguments.  New; the reference has one entry point
+ * (marlin_kernel.h:39-55). */
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, const void *s, int m,
+                                         int n, int k, int groupsize, void *workspace,
+                                         size_t workspace_bytes, void *stream);
+
+/* Scratch bytes the GEMM needs for (m, n, k); replaces the reference wrapper's
+ * fixed `(n/128) * 16` int32 lock array (crates/kiln-marlin-gemm/src/lib.rs:176-178). */
+size_t kiln_w4a16_workspace_bytes(int m, int n, int k);
+
+/* Shape rule of the path (crates/kiln-model/src/marlin_proj.rs:53-55): 1 if supported. */
+int kiln_w4a16_shape_is_supported(int k, int n);
+
+/* ---- packer (crates/kiln-marlin-gemm/src/lib.rs:284-529, `mod pack`) ------------ */
+
+/* pack::build_weight_perm / build_scale_perm / build_scale_perm_single
+ * (lib.rs:296-327, 333-341, 348-357).  out: 1024 / 64 / 32 int32. */
+void kiln_w4a16_build_weight_perm(int32_t *out);
+void kiln_w4a16_build_scale_perm(int32_t *out);
+void kiln_w4a16_build_scale_perm_single(int32_t *out);
+
+/* pack::quantize_and_pack on the HOST (lib.rs:370-491), multi-threaded inside one
+ * matrix.  weight: f32 [k,n] row-major (host).  Outputs (host): b_packed int32
+ * [k/16, 2n]; scales fp16 bits [k/g, n] (Marlin order); dequant f32 [k,n] or NULL.
+ * num_threads <= 0 means "all hardware threads".  Bit-exact with the reference. */
+kiln_w4a16_status_t kiln_w4a16_quantize_and_pack_host(const float *weight, int k, int n, int groupsize,
+                                                      int32_t *b_packed, uint16_t *scales_f16,
+                                                      float *dequant, int num_threads);
+
+/* The same on the DEVICE, straight from the bf16 or f32 [k,n] weight already in HBM
+ * (replaces the download -> CPU pack -> upload round trip of
+ * crates/kiln-model/src/marlin_proj.rs:87-182).  weight_is_bf16: 1 = bf16, 0 = f32.
+ * dequant may be NULL.  Stream-ordered. */
+kiln_w4a16_status_t kiln_w4a16_quantize_and_pack_device(const void *weight, int weight_is_bf16, int k,
+                                                        int n, int groupsize, int32_t *b_packed,
+                                                        uint16_t *scales_f16, float *dequant,
+                                                        void *stream);
+
+/* Steps 3-5 only (lib.rs:429-488) for already-quantised weights: q uint8 [k,n] with
+ * values 0..15, scales fp16 bits [k/g, n] in natural column order -> Marlin layout.
+ * Host and device variants. */
+kiln_w4a16_status_t kiln_w4a16_repack_host(const uint8_t *q, const uint16_t *scales, int k, int n,
+                                           int groupsize, int32_t *b_packed, uint16_t *scales_perm,
+                                           int num_threads);
+kiln_w4a16_status_t kiln_w4a16_repack_device(const uint8_t *q, const uint16_t *scales, int k, int n,
+                                             int groupsize, int32_t *b_packed, uint16_t *scales_perm,
+                                             void *stream);
+
+/* ---- diagnostics --------------------------------------------------------------- */
+
+/* Last CUDA error code seen by this library on the calling thread (0 = none). */
+int kiln_w4a16_last_cuda_error(void);
+
+/* Reads and clears the device status word that bounded device-side waits write
+ * when they give up.  Synchronises `stream`.  Returns KILN_W4A16_OK or
+ * KILN_W4A16_ERR_TIMEOUT; *detail (optional) receives the raw word. */
+kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detail);
+
+/* Tuning hook for sweeps: force the decode kernel's decomposition (cluster size
+ * along K, K-warps and N-warps per CTA).  Pass 0,0,0 to restore the heuristic.
+ * Process-wide, not thread-safe; has no counterpart in the reference. */
+void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
+
+/* Tuning hook: the M at and above which the tcgen05 prefill kernel is used
+ * (default 128).  <= 0 restores the default; a huge value disables that kernel. */
+void kiln_w4a16_set_prefill_min_m(int min_m);
+
+/* Library version, and number of kernels this library launched since load
+ * (diagnostic: lets a harness prove the native path ran). */
+int kiln_w4a16_version(void);
+unsigned long long kiln_w4a16_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif

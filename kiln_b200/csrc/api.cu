@@ -1,0 +1,163 @@
+// C ABI, argument validation and kernel selection for the W4A16 GEMM.
+//
+// Mirrors, under the C boundary, what the reference does in its Rust wrapper
+// (kiln-marlin-gemm/src/lib.rs:97-275: shape and groupsize checks, workspace sizing,
+// status mapping) and in its host dispatcher (kiln-marlin-gemm/csrc/marlin_kernel.cu:731-819:
+// shape -> kernel/tile choice), so that both are testable without a Rust toolchain.
+#include <atomic>
+#include <mutex>
+
+#include "w4a16_common.cuh"
+
+namespace kiln {
+
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+thread_local int t_last_cuda_error = 0;
+DecodeOverride g_decode_override{0, 0, 0};
+std::atomic<int> g_prefill_min_m{128};
+constexpr int kDefaultPrefillMinM = 128;
+}  // namespace
+
+void note_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int record_cuda_error(cudaError_t e) {
+    if (e == cudaSuccess) return 0;
+    t_last_cuda_error = static_cast<int>(e);
+    (void)cudaGetLastError();  // clear the sticky-less error so the next call starts clean
+    return KILN_W4A16_ERR_CUDA;
+}
+
+int device_sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        cached[dev] = sms;
+    }
+    return cached[dev];
+}
+
+// One status word per device, in its own small allocation made on first use (outside any
+// stream capture: call the GEMM once before capturing).
+uint32_t *device_status_word() {
+    static uint32_t *words[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!words[dev]) {
+        uint32_t *p = nullptr;
+        if (record_cuda_error(cudaMalloc(&p, 256))) return nullptr;
+        if (record_cuda_error(cudaMemset(p, 0, 256))) return nullptr;
+        words[dev] = p;
+    }
+    return words[dev];
+}
+
+static int validate(const GemmArgs &a) {
+    if (a.m < 0 || a.n < 0 || a.k < 0) return KILN_W4A16_ERR_ARG;
+    // kiln-marlin-gemm/src/lib.rs:112-117, 128-142
+    if (a.k % 128 != 0 || a.n % 256 != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+    if (!(a.groupsize == -1 || a.groupsize == 128)) return KILN_W4A16_ERR_PROB_SHAPE;
+    if (a.m == 0 || a.n == 0 || a.k == 0) return KILN_W4A16_OK;  // marlin_kernel.cu:772-773
+    if (!a.A || !a.B || !a.C || !a.S) return KILN_W4A16_ERR_ARG;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.B) |
+                           reinterpret_cast<uintptr_t>(a.C) | reinterpret_cast<uintptr_t>(a.S) |
+                           reinterpret_cast<uintptr_t>(a.workspace);
+    if (bits & 15) return KILN_W4A16_ERR_ALIGNMENT;
+    return -1;  // proceed
+}
+
+static bool use_prefill(int m, int n, int k, int groupsize) {
+    return m >= g_prefill_min_m.load(std::memory_order_relaxed) && prefill_supported(m, n, k, groupsize);
+}
+
+static int gemm(const GemmArgs &a) {
+    const int v = validate(a);
+    if (v >= 0) return v;
+    if (use_prefill(a.m, a.n, a.k, a.groupsize)) {
+        const size_t need = prefill_workspace_bytes(a.m, a.n, a.k);
+        if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
+        return launch_prefill(a);
+    }
+    return launch_decode(a, g_decode_override);
+}
+
+}  // namespace kiln
+
+using namespace kiln;
+
+extern "C" {
+
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, const void *s, int m, int n,
+                                         int k, int groupsize, void *workspace, size_t workspace_bytes,
+                                         void *stream) {
+    GemmArgs a{A, B, s, C, m, n, k, groupsize, workspace, workspace_bytes, static_cast<cudaStream_t>(stream)};
+    return gemm(a);
+}
+
+kiln_w4a16_status_t kiln_marlin_w4a16_gemm(const void *A, const void *B, void *C, void *s, int prob_m,
+                                           int prob_n, int prob_k, void *workspace, int groupsize, int dev,
+                                           void *stream, int thread_k, int thread_n, int sms, int max_par) {
+    (void)dev;
+    (void)sms;
+    (void)max_par;
+    // The reference rejects tile overrides the problem is not a multiple of
+    // (marlin_kernel.cu:770-771) and tuples it has no kernel for (:811-812).
+    if (thread_k != -1 || thread_n != -1) {
+        const bool known = (thread_k == 128 && thread_n == 128) || (thread_k == 64 && thread_n == 256);
+        if (thread_k <= 0 || thread_n <= 0) return KILN_W4A16_ERR_KERN_SHAPE;
+        if (prob_n % thread_n != 0 || prob_k % thread_k != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+        if (!known) return KILN_W4A16_ERR_KERN_SHAPE;
+    }
+    // The legacy signature carries no size: the contract is that the caller sized the
+    // buffer with kiln_w4a16_workspace_bytes().
+    const size_t need = kiln_w4a16_workspace_bytes(prob_m, prob_n, prob_k);
+    GemmArgs a{A, B, s, C, prob_m, prob_n, prob_k, groupsize, workspace, workspace ? need : 0,
+               static_cast<cudaStream_t>(stream)};
+    return gemm(a);
+}
+
+size_t kiln_w4a16_workspace_bytes(int m, int n, int k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    if (use_prefill(m, n, k, 128)) return prefill_workspace_bytes(m, n, k);
+    return 0;
+}
+
+int kiln_w4a16_shape_is_supported(int k, int n) { return k > 0 && n > 0 && k % 128 == 0 && n % 256 == 0; }
+
+int kiln_w4a16_last_cuda_error(void) { return t_last_cuda_error; }
+
+kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detail) {
+    uint32_t *w = device_status_word();
+    if (!w) return KILN_W4A16_ERR_CUDA;
+    uint32_t host = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int rc = record_cuda_error(cudaMemcpyAsync(&host, w, sizeof(host), cudaMemcpyDeviceToHost, st))) return rc;
+    if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
+    if (detail) *detail = host;
+    if (host != 0) {
+        if (int rc = record_cuda_error(cudaMemsetAsync(w, 0, sizeof(uint32_t), st))) return rc;
+        if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
+        return KILN_W4A16_ERR_TIMEOUT;
+    }
+    return KILN_W4A16_OK;
+}
+
+void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n) {
+    g_decode_override = DecodeOverride{cluster_k, warps_k, warps_n};
+}
+
+void kiln_w4a16_set_prefill_min_m(int min_m) {
+    g_prefill_min_m.store(min_m > 0 ? min_m : kDefaultPrefillMinM, std::memory_order_relaxed);
+}
+
+int kiln_w4a16_version(void) { return 100; }
+
+unsigned long long kiln_w4a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,89 @@
+"""Mirror of kiln's caller-side helpers (kiln-model/src/marlin_proj.rs)."""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from .marlin_gemm import KilnMarlinError, marlin_w4a16_gemm
+
+
+@dataclass
+class MarlinPackedProj:
+    """marlin_proj.rs:38-50."""
+
+    b_packed: torch.Tensor  # [k/16, 2n] int32, Marlin layout
+    scales: torch.Tensor  # [k/g, n] float16, Marlin order
+    groupsize: int  # -1 or 128
+    k: int
+    n: int
+
+
+def shape_is_supported(k: int, n: int) -> bool:
+    """marlin_proj.rs:53-55."""
+    return k % 128 == 0 and n % 256 == 0
+
+
+def w4a16_enabled() -> bool:
+    """marlin_proj.rs:330-338: KILN_W4A16 in {1, true, yes} (case-insensitive)."""
+    return os.environ.get("KILN_W4A16", "").strip().lower() in ("1", "true", "yes")
+
+
+def pack_from_bf16(weight_t: torch.Tensor, groupsize: int = 128) -> Optional[MarlinPackedProj]:
+    """marlin_proj.rs:198-227: pack a pre-transposed [k, n] weight living on the GPU.
+
+    Returns None for an unsupported shape or a non-CUDA tensor (caller keeps its bf16 path).
+    Unlike the reference's download -> CPU pack -> upload (marlin_proj.rs:87-182) the
+    quantise+pack runs on the device, straight from the tensor.
+    """
+    if not weight_t.is_cuda:
+        return None
+    if weight_t.dim() != 2:
+        raise KilnMarlinError("marlin_proj: weight_t must be a 2D [k, n] tensor")
+    k, n = weight_t.shape
+    if not shape_is_supported(k, n):
+        return None
+    if not (groupsize == -1 or groupsize == 128):
+        raise KilnMarlinError(f"marlin_proj: groupsize must be -1 or 128 (got {groupsize})")
+    if weight_t.dtype not in (torch.bfloat16, torch.float32):
+        weight_t = weight_t.to(torch.float32)
+    w = weight_t.contiguous()
+    g = k if groupsize == -1 else groupsize
+    dev = w.device
+    b_packed = torch.empty((k // 16, 2 * n), dtype=torch.int32, device=dev)
+    scales = torch.empty((k // g, n), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().kiln_w4a16_quantize_and_pack_device(
+            w.data_ptr(), 1 if w.dtype == torch.bfloat16 else 0, k, n, groupsize,
+            b_packed.data_ptr(), scales.data_ptr(), None, torch.cuda.current_stream(dev).cuda_stream,
+        )
+    if rc != 0:
+        raise KilnMarlinError(f"marlin_proj: device pack failed: {_lib.STATUS_NAMES.get(rc, rc)}")
+    return MarlinPackedProj(b_packed, scales, groupsize, k, n)
+
+
+def pack_from_bf16_batch(weights: Sequence[torch.Tensor], groupsize: int = 128):
+    """marlin_proj.rs:229-262: pack many projections; order preserved, None where unsupported."""
+    return [pack_from_bf16(w, groupsize) for w in weights]
+
+
+def matmul_bf16(x: torch.Tensor, proj: MarlinPackedProj) -> torch.Tensor:
+    """marlin_proj.rs:285-319: x [.., k] bf16 -> [.., n] bf16 (rank 2 or 3)."""
+    if x.dim() == 2:
+        lead = None
+        if x.shape[1] != proj.k:
+            raise KilnMarlinError(f"marlin_proj: x last dim {x.shape[1]} != k={proj.k}")
+        x2 = x
+    elif x.dim() == 3:
+        b, s, kk = x.shape
+        if kk != proj.k:
+            raise KilnMarlinError(f"marlin_proj: x last dim {kk} != k={proj.k}")
+        lead = (b, s)
+        x2 = x.reshape(b * s, kk)
+    else:
+        raise KilnMarlinError(f"marlin_proj: matmul_bf16 expects rank-2 or rank-3 input, got rank {x.dim()}")
+    out = marlin_w4a16_gemm(x2.contiguous(), proj.b_packed, proj.scales, proj.groupsize)
+    return out if lead is None else out.reshape(lead[0], lead[1], proj.n)

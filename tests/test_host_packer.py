@@ -1,0 +1,79 @@
+"""Native host packer (C ABI) against the oracle: bit-exact, including digests of full-size matrices."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle import C
+from kiln_b200 import _lib, pack
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _digest(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def test_perm_tables_match_oracle():
+    assert pack.build_weight_perm() == C.weight_perm().tolist()
+    assert pack.build_scale_perm() == C.scale_perm().tolist()
+    assert pack.build_scale_perm_single() == C.scale_perm_single().tolist()
+    assert pack.MAX_Q == 15 and pack.Q_OFFSET == 8
+
+
+@pytest.mark.parametrize("k,n,gs", [(128, 256, 128), (128, 256, -1), (256, 512, 128), (640, 768, 128), (512, 256, -1)])
+@pytest.mark.parametrize("threads", [1, 0])
+def test_quantize_and_pack_bit_exact(k, n, gs, threads):
+    rng = np.random.default_rng(k + n)
+    w = (rng.standard_normal((k, n)) * 0.2).astype(np.float32)
+    w[:, 1] = 0
+    w[3, :] *= 50
+    p, s, d = pack.quantize_and_pack(w, k, n, gs, num_threads=threads)
+    p2, s2, d2, _ = C.quantize_and_pack(w, gs)
+    assert (p == p2).all() and (s.view(np.uint16) == s2.view(np.uint16)).all() and (d == d2).all()
+
+
+def test_full_size_digests():
+    from tests.golden.make_pack_hashes import CASES, synth_weight
+
+    with open(os.path.join(GOLD, "pack_hashes.json")) as f:
+        gold = json.load(f)
+    for k, n, gs, seed in CASES:
+        p, s, d = pack.quantize_and_pack(synth_weight(k, n, seed), k, n, gs)
+        g = gold[f"{k}x{n}_g{gs}_s{seed}"]
+        assert _digest(p) == g["packed"], (k, n, gs)
+        assert _digest(s.view(np.uint16)) == g["scales"] and _digest(d) == g["dequant"]
+
+
+def test_reference_lcg_inputs():
+    # the reference parity test's own weight generator and seeds (parity.rs:33-43, 55)
+    k, n = 128, 256
+    w = oracle.kiln_lcg_fill(k * n, 0xC0FFEE_5EED ^ k ^ (n << 16), 0.5).reshape(k, n)
+    p, s, d = pack.quantize_and_pack(w, k, n, 128)
+    p2, s2, d2, _ = C.quantize_and_pack(w, 128)
+    assert (p == p2).all() and (s.view(np.uint16) == s2.view(np.uint16)).all() and (d == d2).all()
+
+
+def test_repack_prequantised():
+    a, q, s = oracle.synth_inputs(1, 2560, 512, seed=3)
+    p, sp = pack.repack(q, s, 128)
+    assert (p == C.pack_nibbles(q)).all()
+    assert (sp.view(np.uint16) == C.permute_scales(s, 128).view(np.uint16)).all()
+    assert (C.unpack_fragment(p, 2560, 512) == q).all()
+
+
+def test_rejects_what_the_reference_asserts():
+    w = np.zeros((100, 256), np.float32)
+    with pytest.raises(AssertionError):
+        pack.quantize_and_pack(w, 100, 256, 128)  # k % 128
+    with pytest.raises(AssertionError):
+        pack.quantize_and_pack(np.zeros((128, 200), np.float32), 128, 200, 128)  # n % 256
+    with pytest.raises(AssertionError):
+        pack.quantize_and_pack(np.zeros((256, 256), np.float32), 256, 256, 96)  # k % g
+    lib = _lib.lib()
+    out = np.zeros(16, np.int32)
+    assert lib.kiln_w4a16_quantize_and_pack_host(None, 128, 256, 128, out.ctypes.data, out.ctypes.data, None, 1) == _lib.ERR_ARG
+    assert lib.kiln_w4a16_quantize_and_pack_host(out.ctypes.data, 120, 256, 128, out.ctypes.data, out.ctypes.data, None, 1) == _lib.ERR_PROB_SHAPE

@@ -1,7 +1,576 @@
-// placeholder until the tcgen05 kernel lands
+// Prefill-shape W4A16 GEMM for sm_100a: TMA-fed tcgen05 (UMMA) GEMM with TMEM accumulators
+// and the int4 -> bf16 dequant fused into the shared-memory staging of the B operand.
+//
+// Replaces the reference's `Marlin<256,{1..4},16,4,4,8>` path
+// (kiln-marlin-gemm/csrc/marlin_kernel.cu:197-700, dispatch :784-816: 64-row m-tiles,
+// mma.sync, host loop over M) with a persistent, warp-specialised kernel:
+//
+//   warp 0      TMA producer: activation tiles A[128 x 64] bf16 -> 128B-swizzled smem
+//   warp 1      MMA issuer: tcgen05.mma 128 x BN x 16, fp32 accumulators in TMEM (two buffers);
+//               also owns the TMEM allocation
+//   warps 2-5   epilogue: tcgen05.ld TMEM -> registers -> bf16 -> global (or fp32 split-K slabs)
+//   warps 6-13  dequant: packed int4 words (16 B per lane, straight from global/L2) ->
+//               bf16 (nib-8)*scale -> the K-major 128B-swizzled B tile the MMA reads
+//
+// The Marlin fragment layout maps onto the swizzled K-major tile with conflict-free 4-byte
+// stores: lane (qd, c) owns K-pairs (2qd, 2qd+1), (2qd+8, 2qd+9) of column 8t + c, and the
+// 128B swizzle XORs the 16-byte chunk index with (column % 8) = c.
+//
+// Every wait in the kernel is bounded: a wait that runs out records an error code in the
+// device status word, raises a CTA-wide abort flag that every other wait polls, and the CTA
+// drains its outstanding TMA copies, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "w4a16_common.cuh"
+
 namespace kiln {
-bool prefill_supported(int, int, int, int) { return false; }
-size_t prefill_workspace_bytes(int, int, int) { return 0; }
-int launch_prefill(const GemmArgs &) { return KILN_W4A16_ERR_KERN_SHAPE; }
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kNumThreads = 14 * 32;
+constexpr int kDequantWarp0 = 6;
+constexpr int kNumDequantThreads = 8 * 32;
+constexpr int kNumEpilogueThreads = 4 * 32;
+constexpr uint32_t kSpinLimit = 4u << 20;  // polls per wait; each poll may block ~a microsecond or more
+
+struct PrefillParams {
+    const uint4 *B;
+    const __half *S;
+    __nv_bfloat16 *C;
+    float *partial;  // fp32 [splits][m][n] when splits > 1
+    uint32_t *status;
+    int m, n, k;
+    int m_tiles, n_tiles, splits, k_iters;  // k_iters = k / 64
+    int per_column;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false if the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0u, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128B-swizzled operand tile: rows of 64 bf16 (128 B), 8-row atoms 1024 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
+    d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused for swizzled K-major)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset: 8 rows * 128 B
+    d |= static_cast<uint64_t>(1) << 46;                      // descriptor version for sm_100
+    d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+    return d;
+}
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = BM * BK * 2;  // 16 KB
+    static constexpr int kBBytes = BN * BK * 2;  // 32 / 16 KB
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kBlocksPerStage = (BN / 64) * 4;  // 512-byte packed blocks per stage
+    static constexpr int kBlocksPerWarp = kBlocksPerStage / 8;
+    static constexpr int kBarrierBytes = 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+    // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
+    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                       (static_cast<uint32_t>(BM >> 4) << 24);
+};
+
+struct DequantRegs {
+    uint4 w[2];
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
+    auto full_a = [&](int s) { return bar_base + 8u * s; };
+    auto full_b = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+    auto empty = [&](int s) { return bar_base + 8u * (2 * C::kStages + s); };
+    auto tmem_full = [&](int a) { return bar_base + 8u * (3 * C::kStages + a); };
+    auto tmem_empty = [&](int a) { return bar_base + 8u * (3 * C::kStages + 2 + a); };
+    uint8_t *bar_gen = smem_gen + C::kStages * C::kStageBytes;
+    volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bar_gen + 8 * (3 * C::kStages + 4));
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bar_gen + 8 * (3 * C::kStages + 4) + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full_a(s), 1);
+            mbar_init(full_b(s), kNumDequantThreads);
+            mbar_init(empty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tmem_full(a), 1);
+            mbar_init(tmem_empty(a), kNumEpilogueThreads);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t *>(tmem_ptr_slot))),
+                     "r"(static_cast<uint32_t>(C::kTmemCols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_slot;
+
+    const int units = p.m_tiles * p.n_tiles * p.splits;
+    const int chunks_n = p.n >> 6;
+
+    // unit -> (m_tile, n_tile, split, k-iteration range)
+    auto decode_unit = [&](int u, int &mt, int &nt, int &sp, int &ki0, int &ki1) {
+        sp = u % p.splits;
+        const int t = u / p.splits;
+        mt = t % p.m_tiles;
+        nt = t / p.m_tiles;
+        ki0 = static_cast<int>(static_cast<long long>(p.k_iters) * sp / p.splits);
+        ki1 = static_cast<int>(static_cast<long long>(p.k_iters) * (sp + 1) / p.splits);
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                int mt, nt, sp, ki0, ki1;
+                decode_unit(u, mt, nt, sp, ki0, ki1);
+                for (int ki = ki0; ki < ki1; ++ki, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x100u | s))) break;
+                    mbar_arrive_expect_tx(full_a(s), C::kABytes);
+                    tma_load_2d(smem_base + s * C::kStageBytes, &tmap_a, ki * BK, mt * BM, full_a(s));
+                }
+            }
+            if (!ok) {
+                // drain: wait (bounded, ignoring the abort flag) for copies already issued
+                const uint32_t first = it >= static_cast<uint32_t>(C::kStages) ? it - C::kStages : 0;
+                for (uint32_t j = first; j < it; ++j) {
+                    const int s = j % C::kStages;
+                    const uint32_t ph = (j / C::kStages) & 1;
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(full_a(s), ph); ++i) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, tile = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
+                int mt, nt, sp, ki0, ki1;
+                decode_unit(u, mt, nt, sp, ki0, ki1);
+                const uint32_t acc = tile & 1, acc_ph = (tile >> 1) & 1;
+                if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int ki = ki0; ki < ki1; ++ki, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s))) break;
+                    if (!(ok = mbar_wait(full_b(s), ph, abort_flag, p.status, 0x400u | s))) break;
+                    tc_fence_after();
+                    const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes);
+                    const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes);
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)
+                        umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, C::kIdesc, (ki > ki0 || kk > 0) ? 1u : 0u);
+                    umma_commit(empty(s));  // frees the stage when these MMAs have read it
+                }
+                if (ok) umma_commit(tmem_full(acc));
+            }
+        }
+    } else if (warp < kDequantWarp0) {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+        uint32_t tile = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
+            int mt, nt, sp, ki0, ki1;
+            decode_unit(u, mt, nt, sp, ki0, ki1);
+            const uint32_t acc = tile & 1, acc_ph = (tile >> 1) & 1;
+            if (!(ok = mbar_wait(tmem_full(acc), acc_ph, abort_flag, p.status, 0x500u | acc))) break;
+            tc_fence_after();
+            const int row = mt * BM + quarter * 32 + lane;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                tmem_ld_wait();
+                if (row < p.m) {
+                    const int col = nt * BN + cc * 32;
+                    if (p.splits == 1) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(row) * p.n + col);
+                        float sc[2] = {1.f, 1.f};
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float x0 = __uint_as_float(r[8 * v + 2 * e]), x1 = __uint_as_float(r[8 * v + 2 * e + 1]);
+                                if (p.per_column) {
+                                    const int pos = scale_single_pos(col + 8 * v + 2 * e);
+                                    sc[0] = __half2float(p.S[pos]);
+                                    sc[1] = __half2float(p.S[pos + 1]);
+                                    x0 *= sc[0];
+                                    x1 *= sc[1];
+                                }
+                                __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
+                                o[e] = *reinterpret_cast<uint32_t *>(&b);
+                            }
+                            dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    } else {
+                        float4 *dst = reinterpret_cast<float4 *>(
+                            p.partial + (static_cast<size_t>(sp) * p.m + row) * p.n + col);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tmem_empty(acc));
+        }
+    } else {
+        // ---------------- dequant: packed int4 -> bf16 B tile ----------------
+        const int dw = warp - kDequantWarp0;
+        const int qd = lane & 3, c = lane >> 2;
+        constexpr int kChunksPerTile = BN / 64;
+        uint32_t it = 0;
+        bool ok = true;
+        int cur_group = -1;
+        uint32_t s2[8];  // bf16x2 {s, s} for columns 8t + c of this warp's chunk
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            int mt, nt, sp, ki0, ki1;
+            decode_unit(u, mt, nt, sp, ki0, ki1);
+            cur_group = -1;
+            auto load_regs = [&](DequantRegs &d, int ki) {
+#pragma unroll
+                for (int b = 0; b < C::kBlocksPerWarp; ++b) {
+                    const int blk = dw + 8 * b;
+                    const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
+                    const size_t idx =
+                        (static_cast<size_t>(ki * 4 + kt) * chunks_n + nt * kChunksPerTile + ch) * 32 + lane;
+                    d.w[b] = ld_stream_v4(p.B + idx);
+                }
+            };
+            DequantRegs r0, r1;
+            load_regs(r0, ki0);
+            if (ki0 + 1 < ki1) load_regs(r1, ki0 + 1);
+            for (int ki = ki0; ki < ki1; ++ki, ++it) {
+                const int s = it % C::kStages;
+                const uint32_t ph = (it / C::kStages) & 1;
+                // scales of this K group (all blocks of a warp share one chunk: blk % kChunksPerTile == dw % ..)
+                const int g = p.per_column ? 0 : (ki >> 1);
+                if (g != cur_group) {
+                    cur_group = g;
+                    if (p.per_column) {
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) s2[t] = 0x3F803F80u;  // bf16x2 {1, 1}; scale applied in the epilogue
+                    } else {
+                        const int ch = dw % kChunksPerTile;
+                        const uint4 sv = ld_stream_v4(reinterpret_cast<const uint4 *>(
+                            p.S + static_cast<size_t>(g) * p.n + (nt * kChunksPerTile + ch) * 64 + 8 * c));
+                        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            const float f = __half2float(__ushort_as_half(
+                                static_cast<unsigned short>((t & 1) ? (sw[t >> 1] >> 16) : (sw[t >> 1] & 0xFFFFu))));
+                            __nv_bfloat162 b = __floats2bfloat162_rn(f, f);
+                            s2[t] = *reinterpret_cast<uint32_t *>(&b);
+                        }
+                    }
+                }
+                if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x600u | s))) break;
+                const uint32_t b_tile = smem_base + s * C::kStageBytes + C::kABytes;
+#pragma unroll
+                for (int b = 0; b < C::kBlocksPerWarp; ++b) {
+                    const int blk = dw + 8 * b;
+                    const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
+                    const uint32_t xs[4] = {r0.w[b].x, r0.w[b].y, r0.w[b].z, r0.w[b].w};
+                    // row (= column of B) n_local = ch*64 + 8t + c, 128 B per row; 16-byte chunk (2kt + half) ^ c
+                    const uint32_t row_base = b_tile + static_cast<uint32_t>(ch * 64 + c) * 128u + 4u * qd;
+                    const uint32_t sw_lo = static_cast<uint32_t>((2 * kt) ^ c) << 4;
+                    const uint32_t sw_hi = static_cast<uint32_t>((2 * kt + 1) ^ c) << 4;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t x = xs[j];
+                        uint32_t v[4];
+                        v[0] = lop3_and_or(x, kNibMask, kMagic128);        // K 2qd, 2qd+1     col 16j + c
+                        v[1] = lop3_and_or(x >> 4, kNibMask, kMagic128);   // K 2qd+8, 2qd+9   col 16j + c
+                        v[2] = lop3_and_or(x >> 8, kNibMask, kMagic128);   // K 2qd, 2qd+1     col 16j + 8 + c
+                        v[3] = lop3_and_or(x >> 12, kNibMask, kMagic128);  // K 2qd+8, 2qd+9   col 16j + 8 + c
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 w = *reinterpret_cast<__nv_bfloat162 *>(&v[e]);
+                            const uint32_t k136 = kPos136x2;
+                            w = __hsub2(w, *reinterpret_cast<const __nv_bfloat162 *>(&k136));
+                            w = __hmul2(w, *reinterpret_cast<const __nv_bfloat162 *>(&s2[2 * j + (e >> 1)]));
+                            v[e] = *reinterpret_cast<uint32_t *>(&w);
+                        }
+                        const uint32_t r_lo = row_base + static_cast<uint32_t>(16 * j) * 128u;
+                        const uint32_t r_hi = r_lo + 8u * 128u;
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(r_lo + sw_lo), "r"(v[0]) : "memory");
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(r_lo + sw_hi), "r"(v[1]) : "memory");
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(r_hi + sw_lo), "r"(v[2]) : "memory");
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(r_hi + sw_hi), "r"(v[3]) : "memory");
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(full_b(s));
+                r0 = r1;
+                if (ki + 2 < ki1) load_regs(r1, ki + 2);
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(C::kTmemCols))
+                     : "memory");
+    }
+}
+
+// out[m][n] = bf16(sum_s partial[s][m][n]) (* per-column scale)
+__global__ void splitk_reduce_kernel(const float *partial, __nv_bfloat16 *C, const __half *S, int m, int n,
+                                     int splits, int per_column) {
+    const size_t total4 = static_cast<size_t>(m) * n / 4;
+    const size_t slab4 = total4;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total4;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 acc = reinterpret_cast<const float4 *>(partial)[i];
+        for (int s = 1; s < splits; ++s) {
+            const float4 v = reinterpret_cast<const float4 *>(partial)[i + s * slab4];
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        if (per_column) {
+            const int col = static_cast<int>((i * 4) % n);
+            const int p0 = scale_single_pos(col), p1 = scale_single_pos(col + 2);
+            acc.x *= __half2float(S[p0]);
+            acc.y *= __half2float(S[p0 + 1]);
+            acc.z *= __half2float(S[p1]);
+            acc.w *= __half2float(S[p1 + 1]);
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        reinterpret_cast<uint2 *>(C)[i] = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+    }
+}
+
+// ---- host -----------------------------------------------------------------------------------
+
+struct PrefillConfig {
+    int bn, splits;
+};
+
+PrefillConfig choose_prefill(int m, int n, int k) {
+    const int sms = device_sm_count();
+    const int m_tiles = (m + BM - 1) / BM, k_iters = k / BK;
+    PrefillConfig best{256, 1};
+    double best_t = 1e30;
+    const int bns[2] = {256, 128};
+    const int ss[6] = {1, 2, 3, 4, 6, 8};
+    for (int bi = 0; bi < 2; ++bi)
+        for (int si = 0; si < 6; ++si) {
+            const int bn = bns[bi], s = ss[si];
+            if (k_iters / s < 8) continue;
+            const long long units = static_cast<long long>(m_tiles) * (n / bn) * s;
+            const double waves = static_cast<double>((units + sms - 1) / sms);
+            const double t_iter = bn == 256 ? 0.40 : 0.23;  // microseconds per 64-K step, measured order of magnitude
+            double t = waves * (static_cast<double>(k_iters) / s * t_iter + 0.3) + 1.5;
+            if (s > 1) t += 3.0 + (static_cast<double>(s) + 0.5) * m * static_cast<double>(n) * 4.0 * 2.0 / 4.0e6;
+            if (t < best_t) {
+                best_t = t;
+                best = PrefillConfig{bn, s};
+            }
+        }
+    return best;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+template <int BN>
+int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN>,
+                                                            cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
+            return rc;
+        attr_set[dev] = true;
+    }
+    const int units = p.m_tiles * p.n_tiles * p.splits;
+    const int grid = units < device_sm_count() ? units : device_sm_count();
+    note_launch();
+    w4a16_prefill_kernel<BN><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, p);
+    return record_cuda_error(cudaGetLastError());
+}
+
+}  // namespace
+
+bool prefill_supported(int m, int n, int k, int groupsize) {
+    (void)groupsize;
+    return m >= 1 && n % 256 == 0 && k % 128 == 0 && k / BK >= 2;
+}
+
+size_t prefill_workspace_bytes(int m, int n, int k) {
+    const PrefillConfig c = choose_prefill(m, n, k);
+    return c.splits > 1 ? static_cast<size_t>(c.splits) * m * n * sizeof(float) : 0;
+}
+
+int launch_prefill(const GemmArgs &a) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return KILN_W4A16_ERR_CUDA;
+    uint32_t *status = device_status_word();
+    if (!status) return KILN_W4A16_ERR_CUDA;
+    const PrefillConfig c = choose_prefill(a.m, a.n, a.k);
+
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k) * 2};
+    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.A), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return KILN_W4A16_ERR_CUDA;
+
+    PrefillParams p{};
+    p.B = static_cast<const uint4 *>(a.B);
+    p.S = static_cast<const __half *>(a.S);
+    p.C = static_cast<__nv_bfloat16 *>(a.C);
+    p.partial = static_cast<float *>(a.workspace);
+    p.status = status;
+    p.m = a.m;
+    p.n = a.n;
+    p.k = a.k;
+    p.m_tiles = (a.m + BM - 1) / BM;
+    p.n_tiles = a.n / c.bn;
+    p.splits = c.splits;
+    p.k_iters = a.k / BK;
+    p.per_column = a.groupsize == -1;
+    if (c.splits > 1 && (!a.workspace || a.workspace_bytes < static_cast<size_t>(c.splits) * a.m * a.n * sizeof(float)))
+        return KILN_W4A16_ERR_WORKSPACE;
+
+    int rc = c.bn == 256 ? launch_bn<256>(tmap, p, a.stream) : launch_bn<128>(tmap, p, a.stream);
+    if (rc) return rc;
+    if (c.splits > 1) {
+        const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;
+        int blocks = static_cast<int>((total4 + 255) / 256);
+        const int cap = device_sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        note_launch();
+        splitk_reduce_kernel<<<blocks, 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, c.splits, p.per_column);
+        rc = record_cuda_error(cudaGetLastError());
+    }
+    return rc;
+}
+
 }  // namespace kiln

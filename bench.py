@@ -1,0 +1,477 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 quantised-linear path on B200.
+
+Workload (default): the decode sweep -- M in {1,4,8,16} over the eight Qwen3.5-4B-like
+projection shapes = 32 W4A16 GEMMs per step, synthetic seeded inputs with the distributions
+the configuration names (bf16 N(0,1) activations, uniform int4 nibbles, fp16 scales
+0.01*|N(0,1)|+1e-3, group 128).  `value` is algorithmic GB/s (weights + scales + activations
++ outputs, each counted once) over the whole step with everything resident in HBM; weights
+rotate through 8 distinct copies per shape so that every launch streams from HBM, not L2.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]          one JSON line (rank 0)
+  python bench.py --impl reference ...                          the CPU dequantise+matmul path, same line
+  python bench.py --only decode:gate_up:1 --steps 6             one shape, plain launches (for ncu -k)
+  python bench.py --only prefill:down:2048 --steps 3
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SHAPES = {  # name: (k, n)
+    "q": (2560, 4096), "k": (2560, 512), "v": (2560, 512), "o": (4096, 2560),
+    "gate_up": (2560, 18432), "down": (9216, 2560), "gdn_in": (2560, 8192), "gdn_out": (4096, 2560),
+}
+DECODE_MS = (1, 4, 8, 16)
+PREFILL = [(m, s) for s in ("gate_up", "down") for m in (512, 2048, 8192)]
+ROT = 8  # distinct weight copies per shape
+SEED = 1234
+L2_BYTES = 126e6
+
+
+def alg_bytes(m, k, n):
+    return k * n / 2 + (k // 128) * n * 2 + m * k * 2 + m * n * 2
+
+
+def alg_flops(m, k, n):
+    return 2.0 * m * n * k
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's CPU dequantise(bf16)-then-matmul path, all host threads
+# ----------------------------------------------------------------------------------------------
+def cpu_sweep_inputs():
+    import numpy as np
+
+    import oracle
+
+    cases = []
+    for mi, m in enumerate(DECODE_MS):
+        for name, (k, n) in SHAPES.items():
+            a, q, s = oracle.synth_inputs(m, k, n, seed=SEED + 17 * mi + len(name))
+            cases.append((a, q, s, np.empty((k, n), np.uint16)))
+    return cases
+
+
+def cpu_sweep_once(cases):
+    from oracle import C
+
+    t0 = time.perf_counter()
+    for a, q, s, scratch in cases:
+        C.gemm_cpu_reference(a, q, s, 128, scratch)
+    return time.perf_counter() - t0
+
+
+def sweep_bytes():
+    return sum(alg_bytes(m, *SHAPES[s]) for m in DECODE_MS for s in SHAPES)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from oracle import C
+
+    oracle.build()
+    cases = cpu_sweep_inputs()
+    for _ in range(max(args.warmup, 1) if args.warmup else 0):
+        cpu_sweep_once(cases)
+    times = [cpu_sweep_once(cases) for _ in range(args.steps)]
+    total = sum(times)
+    value = sweep_bytes() * args.steps / total / 1e9
+    cores = C.num_threads()
+    sample = "every step = the full 32-GEMM decode sweep (M in 1,4,8,16 x 8 shapes), dequantise to bf16 then f32 matmul"
+    line = {
+        "impl": "reference", "metric": "w4a16_decode_sweep_algorithmic_GBps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "kiln's packer/wrapper are Rust (no toolchain here): this arm is the C restatement of its CPU "
+                "dequantise-then-matmul convention (oracle/w4a16_oracle.c) on all host threads",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config():
+    return {
+        "workload": "decode sweep: M in {1,4,8,16} x {q 2560->4096, k 2560->512, v 2560->512, o 4096->2560, "
+                    "gate+up 2560->18432, down 9216->2560, GDN-in 2560->8192, GDN-out 4096->2560}; int4 group-128, "
+                    "fp16 scales, bf16 activations; 32 GEMMs per step",
+        "l2": f"weights rotate through {ROT} distinct copies per shape (504 MB between reuses, L2 is 126 MB)",
+        "seed": SEED,
+    }
+
+
+# ----------------------------------------------------------------------------------------------
+# device side
+# ----------------------------------------------------------------------------------------------
+class Device:
+    def __init__(self, local_rank: int):
+        import torch
+
+        import kiln_b200
+        from kiln_b200 import _lib
+
+        self.torch, self.k, self.lib = torch, kiln_b200, _lib.lib()
+        self.dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(self.dev)
+        self.gen = torch.Generator(device=self.dev)
+        self.gen.manual_seed(SEED + local_rank)
+
+    def weights(self, k, n, copies):
+        t = self.torch
+        out = []
+        for _ in range(copies):
+            b = t.randint(-2 ** 31, 2 ** 31 - 1, (k // 16, 2 * n), dtype=t.int32, device=self.dev, generator=self.gen)
+            s = (0.01 * t.randn((k // 128, n), device=self.dev, generator=self.gen).abs() + 1e-3).to(t.float16)
+            out.append((b, s))
+        return out
+
+    def acts(self, m, k):
+        t = self.torch
+        return t.randn((m, k), device=self.dev, generator=self.gen).to(t.bfloat16)
+
+    def gemm(self, a, w, out):
+        return self.k.marlin_w4a16_gemm(a, w[0], w[1], 128, out=out)
+
+    def time_graph(self, fn, launches, reps=10, warm=3):
+        """Median microseconds per launch of `fn` captured once in a CUDA graph."""
+        t = self.torch
+        fn()
+        t.cuda.synchronize()
+        g = t.cuda.CUDAGraph()
+        with t.cuda.graph(g):
+            fn()
+        for _ in range(warm):
+            g.replay()
+        t.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            t.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / launches)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+
+def decode_detail(d: Device, peaks):
+    """Per-shape microseconds, GB/s and fraction of the measured HBM peak (M = 1 and 16)."""
+    out = {}
+    for name, (k, n) in SHAPES.items():
+        copies = max(2, min(64, int(2.2 * L2_BYTES / (k * n / 2)) + 1))
+        ws = d.weights(k, n, copies)
+        for m in (1, 16):
+            a = d.acts(m, k)
+            o = d.torch.empty((m, n), dtype=d.torch.bfloat16, device=d.dev)
+            nl = max(copies, 32)
+
+            def fn():
+                for i in range(nl):
+                    d.gemm(a, ws[i % copies], o)
+
+            us = d.time_graph(fn, nl, reps=7)
+            gbs = alg_bytes(m, k, n) / us / 1e3
+            out[f"{name}:m{m}"] = {"us": round(us, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4)}
+        del ws
+    return out
+
+
+def prefill_detail(d: Device, peaks):
+    """Chunked-prefill GEMMs: microseconds, TFLOP/s, fraction of the measured bf16 tensor peak."""
+    out = {}
+    t = d.torch
+    for m, name in PREFILL:
+        k, n = SHAPES[name]
+        ws = d.weights(k, n, 2)
+        a = d.acts(m, k)
+        o = t.empty((m, n), dtype=t.bfloat16, device=d.dev)
+        flush = t.empty(int(160e6), dtype=t.uint8, device=d.dev)
+        for i in range(3):
+            d.gemm(a, ws[i % 2], o)
+        t.cuda.synchronize()
+        ts = []
+        for i in range(7):
+            flush.zero_()  # write a buffer larger than L2 between timed launches
+            e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            e0.record()
+            d.gemm(a, ws[i % 2], o)
+            e1.record()
+            t.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        us = ts[len(ts) // 2]
+        tf = alg_flops(m, k, n) / us / 1e6
+        out[f"{name}:m{m}"] = {"us": round(us, 1), "TFLOPs": round(tf, 1), "frac_bf16_burst": round(tf / peaks["bf16_tflops"], 4),
+                               "frac_bf16_nominal_2250": round(tf / 2250.0, 4)}
+        del ws, a, o, flush
+    return out
+
+
+def run_only(args):
+    """One shape with plain (non-graph) launches over rotating weights: the command ncu profiles."""
+    kind, name, m = args.only.split(":")
+    m = int(m)
+    k, n = SHAPES[name]
+    d = Device(0)
+    t = d.torch
+    copies = max(2, min(64, int(2.2 * L2_BYTES / (k * n / 2)) + 1))
+    ws = d.weights(k, n, copies)
+    a = d.acts(m, k)
+    o = t.empty((m, n), dtype=t.bfloat16, device=d.dev)
+    for i in range(args.warmup):
+        d.gemm(a, ws[i % copies], o)
+    t.cuda.synchronize()
+    e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        d.gemm(a, ws[(i + args.warmup) % copies], o)
+    e1.record()
+    t.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"only": args.only, "us_per_launch_plain": us, "GBps": alg_bytes(m, k, n) / us / 1e3,
+                      "TFLOPs": alg_flops(m, k, n) / us / 1e6, "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = load_peaks()
+    d = Device(local_rank)
+    t = torch
+
+    # ---- resident tensors of the sweep
+    ws = {name: d.weights(k, n, ROT) for name, (k, n) in SHAPES.items()}
+    acts = {(m, kk): d.acts(m, kk) for m in DECODE_MS for kk in {k for k, _ in SHAPES.values()}}
+    outs = {(m, name): t.empty((m, n), dtype=t.bfloat16, device=d.dev) for m in DECODE_MS for name, (_, n) in SHAPES.items()}
+
+    def step(parity):
+        for mi, m in enumerate(DECODE_MS):
+            for name, (k, n) in SHAPES.items():
+                d.gemm(acts[(m, k)], ws[name][(parity * 4 + mi) % ROT], outs[(m, name)])
+
+    step(0)
+    step(1)
+    t.cuda.synchronize()
+    graphs = []
+    launches_per_step = None
+    for parity in (0, 1):
+        g = t.cuda.CUDAGraph()
+        c0 = d.lib.kiln_w4a16_launch_count()
+        with t.cuda.graph(g):
+            step(parity)
+        launches_per_step = int(d.lib.kiln_w4a16_launch_count() - c0)
+        graphs.append(g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        t.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        graphs[i % 2].replay()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # keep the timed region long enough for the clock sampler to see it
+    e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        graphs[i % 2].replay()
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    # a longer untimed run under the same sampler so that clocks are sampled under this load
+    t_end = time.time() + 0.6
+    while time.time() < t_end:
+        for i in range(50):
+            graphs[i % 2].replay()
+        t.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        tt = t.tensor([elapsed_ms], device=d.dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(tt.item())
+    ms_per_step = elapsed_ms / args.steps
+    step_bytes = sweep_bytes()
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers
+    h_in = {(m, kk): acts[(m, kk)].cpu().pin_memory() for (m, kk) in acts}
+    h_out = {key: t.empty(o.shape, dtype=o.dtype).pin_memory() for key, o in outs.items()}
+    d_in = {key: t.empty_like(v, device=d.dev) for key, v in h_in.items()}
+
+    def e2e_step(parity):
+        for mi, m in enumerate(DECODE_MS):
+            for name, (k, n) in SHAPES.items():
+                d_in[(m, k)].copy_(h_in[(m, k)], non_blocking=True)
+                d.gemm(d_in[(m, k)], ws[name][(parity * 4 + mi) % ROT], outs[(m, name)])
+                h_out[(m, name)].copy_(outs[(m, name)], non_blocking=True)
+        t.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i % 2)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i % 2)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        tt = t.tensor([e2e_s], device=d.dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = float(tt.item())
+    h2d = sum(m * SHAPES[s][0] * 2 for m in DECODE_MS for s in SHAPES)
+    d2h = sum(m * SHAPES[s][1] * 2 for m in DECODE_MS for s in SHAPES)
+    e2e_value = world * step_bytes * args.steps / e2e_s / 1e9
+
+    line = {
+        "metric": "w4a16_decode_sweep_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(),
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s / args.steps * 1e3,
+                "how": "kiln_b200.marlin_w4a16_gemm per GEMM: pinned-host activations -> device, GEMM, output -> pinned host"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "roofline": {
+            "bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": value / world / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (MEASURED_PEAKS.json hbm_gbs, copy)",
+            "kernel": "w4a16_decode_kernel", "traffic": None,
+            "per_launch": {"algorithmic_bytes": step_bytes / launches_per_step,
+                           "avg_us": ms_per_step * 1e3 / launches_per_step},
+            "frac_of_nominal_8TBps": value / world / 8000.0,
+        },
+        "us_per_gemm_avg": ms_per_step * 1e3 / 32,
+    }
+    if world > 1:
+        line["note"] = "replicas: every rank runs the sweep on its own tokens (data-parallel serving); no collective in the path"
+
+    if rank == 0 and not args.quick:
+        del h_in, h_out, d_in
+        line["decode"] = decode_detail(d, peaks)
+        line["prefill"] = prefill_detail(d, peaks)
+        if world == 1:
+            cases = cpu_sweep_inputs()
+            cpu_sweep_once(cases)
+            reps = 3
+            ct = sum(cpu_sweep_once(cases) for _ in range(reps)) / reps
+            from oracle import C
+
+            line["cpu_baseline"] = {
+                "value": step_bytes / ct / 1e9, "unit": "GB/s", "cores": C.num_threads(), "kind": "port",
+                "ms_per_step": ct * 1e3,
+                "sample": f"{reps} passes of the full 32-GEMM sweep on the host (dequantise to bf16, f32 matmul)",
+            }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, help="decode:<shape>:<m> or prefill:<shape>:<m>")
+    ap.add_argument("--quick", action="store_true", help="skip the per-shape tables and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.only:
+        run_only(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

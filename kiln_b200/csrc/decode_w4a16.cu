@@ -3,218 +3,262 @@
 // Replaces the reference's `Marlin<256,1,8,8,4,8>` path
 // (kiln-marlin-gemm/csrc/marlin_kernel.cu:197-700) with a different decomposition:
 //
-//  * HBM streaming, GEMV-like: the unit of work is one 4 KB run of the packed matrix
-//    (one 64-column chunk x one 128-row scale group).  A warp reads a unit as eight
-//    coalesced 512-byte loads (16 bytes per lane) that are all in flight at once, and keeps
-//    a second unit in flight while it computes.
-//  * in-register int4 -> bf16 dequant: `lop3` puts each nibble pair into the mantissa of
-//    bf16x2 {128,128}; the "+128+8" offset is not subtracted per weight but removed once per
-//    MMA tile by one extra MMA against a constant -136 fragment.
-//  * bf16 m16n8k16 tensor-core MMAs with fp32 accumulation; the fp16 group scale is applied
-//    once per 128-K group to the fp32 partial sums (exact scale, no bf16 rounding of it).
-//  * split-K without global scratch: the K range is split over the warps of a CTA and over
+//  * HBM streaming, GEMV-like.  The unit of work is one "stage": one 128-row scale group of
+//    WN adjacent 64-column chunks = 8 runs of WN*512 contiguous bytes of the packed matrix
+//    plus WN*128 bytes of scales.  A producer warp moves stages global -> shared with bulk
+//    asynchronous copies (TMA, mbarrier completion) into a ring, so the bytes in flight per SM
+//    are set by the ring depth, not by registers or by how many warps are resident, and the
+//    weight stream starts before the previous kernel in the stream has finished
+//    (programmatic dependent launch; only the activations wait for it).
+//  * consumer warps: in-register int4 -> bf16 dequant (`lop3` puts each nibble pair into the
+//    mantissa of bf16x2 {128,128}; the shifts that align the nibbles are issued as high
+//    multiplies so they run beside the `lop3`s on another pipe); the +128+8 offset is not
+//    subtracted per weight but removed per MMA tile by one extra MMA against a constant
+//    -136 fragment; bf16 m16n8k16 tensor-core MMAs with fp32 accumulation; the fp16 group
+//    scale is applied once per 128-K group to the fp32 partial sums (exact scale).
+//  * split-K without global scratch: K is split over teams of warps inside a CTA and over
 //    the CTAs of a thread-block cluster; partial tiles meet in (distributed) shared memory
 //    and are summed in a fixed order, so results are bit-reproducible.
-//  * programmatic dependent launch: the first weight loads are issued before waiting for
-//    the previous kernel in the stream, so back-to-back GEMMs overlap their ramp-up.
-#include "w4a16_common.cuh"
+//  * every wait on an mbarrier is bounded (see w4a16_async.cuh).
+#include <cstdlib>
+
+#include "w4a16_async.cuh"
 
 namespace kiln {
+namespace {
 
 struct DecodeParams {
     const __nv_bfloat16 *A;
-    const uint4 *B;
+    const uint8_t *B;  // packed weights, byte view
     const __half *S;
     __nv_bfloat16 *C;
+    uint32_t *status;
     int m, n, k;
     int groups;          // k / 128
     int groups_per_cta;  // K groups owned by one CTA of the cluster
-    int pass_groups;     // K groups whose activations are staged in shared memory at a time
     int warps_n, warps_k;
+    int stages;          // ring depth
     int per_column;      // groupsize == -1: one scale row, applied at the end
-    int a_pitch;         // elements per staged activation row (pass_groups*128 + 8)
+    int a_pitch;         // bytes per staged activation row (groups_per_cta*256 + 16)
     int red_pitch;       // floats per reduction row (warps_n*64 + 8)
-    int a_bytes;         // bytes of the activation stage
+    // shared-memory carve-up (bytes from the 128-byte aligned base)
+    int off_ring, off_red, off_bar, stage_bytes;
+    int debug;  // bit0: skip compute, bit1: skip reduce
 };
 
-struct UnitRegs {
-    uint4 w[8];
-    uint4 sc[2];
-};
-
-__device__ __forceinline__ void load_unit(UnitRegs &u, const DecodeParams &p, int g, int chunk,
-                                          int lane) {
-    const int chunks = p.n >> 6;
-    const uint4 *b = p.B + (static_cast<size_t>(g) * 8 * chunks + chunk) * 32 + lane;
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) u.w[kt] = ld_stream_v4(b + static_cast<size_t>(kt) * chunks * 32);
-    if (p.per_column) {
-        u.sc[0] = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);  // fp16 ones
-        u.sc[1] = u.sc[0];
-    } else {
-        // accumulator columns of this lane are chunk*64 + 8t + 2*(lane%4) + e; in the Marlin
-        // scale order those sit at 16*(lane%4) + 8e + t: 32 contiguous bytes.
-        const uint4 *s = reinterpret_cast<const uint4 *>(p.S + static_cast<size_t>(g) * p.n + chunk * 64 +
-                                                         16 * (lane & 3));
-        u.sc[0] = ld_stream_v4(s);
-        u.sc[1] = ld_stream_v4(s + 1);
-    }
+__device__ __forceinline__ float half_bits_to_float(uint32_t w, int hi) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(hi ? (w >> 16) : (w & 0xFFFFu))));
 }
 
-__device__ __forceinline__ float half_at(const uint4 &v, int t) {
-    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-    const uint32_t w = words[t >> 1];
-    return __half2float(__ushort_as_half(static_cast<unsigned short>((t & 1) ? (w >> 16) : (w & 0xFFFFu))));
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
-template <int MT>
-__device__ __forceinline__ void compute_unit(const UnitRegs &u, uint32_t a_addr, uint32_t a_mt_stride,
-                                             float (&acc)[MT][8][4]) {
-    float g[MT][8][4];
-    float corr[MT][4];
+// x >> s as a high multiply (runs on the FMA pipe, beside the lop3s on the ALU pipe)
+template <int S>
+__device__ __forceinline__ uint32_t shr_mul(uint32_t x) {
+    return __umulhi(x, 1u << (32 - S));
+}
+
+// One stage for one warp: 8 K-tiles of one 64-column chunk.
+//
+// The MMA is issued transposed: the weights are its 16x16 "A" operand (16 output columns x 16 K)
+// and the activations its 16x8 "B" operand (16 K x 8 batch rows).  A packed word is exactly
+// one such A fragment -- nibble pairs (0,4) (2,6) (1,5) (3,7) are a0..a3 -- so a batch of up to 8
+// rows costs one MMA per word instead of two, and the accumulators D^T[16 cols x 8 rows] of a
+// lane sit on columns c + 8t, whose eight scales are one 16-byte run of the Marlin scale order.
+template <int NB>
+__device__ __forceinline__ void compute_stage(uint32_t w_addr, uint32_t w_kt_stride, uint32_t s_addr, bool scaled,
+                                              uint32_t a_addr, float (&acc)[4][NB][4]) {
+    float g[4][NB][4];
+    float corr[NB][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) corr[mt][i] = 0.f;
+        for (int i = 0; i < 4; ++i) corr[nb][i] = 0.f;
 #pragma unroll
-        for (int t = 0; t < 8; ++t)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) g[mt][t][i] = 0.f;
+            for (int i = 0; i < 4; ++i) g[j][nb][i] = 0.f;
     }
+    uint4 sc = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);  // fp16 ones
+    if (scaled) sc = lds_v4(s_addr);
+    const uint32_t neg[4] = {kNeg136x2, kNeg136x2, kNeg136x2, kNeg136x2};
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt) {
-        uint32_t a[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(a[mt], a_addr + mt * a_mt_stride + kt * 32);
-        const uint32_t xs[4] = {u.w[kt].x, u.w[kt].y, u.w[kt].z, u.w[kt].w};
+        const uint4 w = lds_v4(w_addr + kt * w_kt_stride);
+        uint32_t b[NB][2];
+        if (NB == 1) {
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                         : "=r"(b[0][0]), "=r"(b[0][1])
+                         : "r"(a_addr + kt * 32));
+        } else {
+            uint32_t r[4];
+            ldmatrix_x4(r, a_addr + kt * 32);
+            b[0][0] = r[0];
+            b[0][1] = r[1];
+            b[NB - 1][0] = r[2];
+            b[NB - 1][1] = r[3];
+        }
+        const uint32_t xs[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t x = xs[j];
-            const uint32_t p0 = lop3_and_or(x, kNibMask, kMagic128);
-            const uint32_t p1 = lop3_and_or(x >> 4, kNibMask, kMagic128);
-            const uint32_t p2 = lop3_and_or(x >> 8, kNibMask, kMagic128);
-            const uint32_t p3 = lop3_and_or(x >> 12, kNibMask, kMagic128);
+            uint32_t f[4];
+            f[0] = lop3_and_or(x, kNibMask, kMagic128);              // col c,   K 2qd, 2qd+1
+            f[2] = lop3_and_or(shr_mul<4>(x), kNibMask, kMagic128);   // col c,   K 2qd+8, 2qd+9
+            f[1] = lop3_and_or(shr_mul<8>(x), kNibMask, kMagic128);   // col c+8, K 2qd, 2qd+1
+            f[3] = lop3_and_or(shr_mul<12>(x), kNibMask, kMagic128);  // col c+8, K 2qd+8, 2qd+9
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                mma_bf16_16816(g[mt][2 * j], a[mt], p0, p1);
-                mma_bf16_16816(g[mt][2 * j + 1], a[mt], p2, p3);
-            }
+            for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(g[j][nb], f, b[nb][0], b[nb][1]);
         }
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(corr[mt], a[mt], kNeg136x2, kNeg136x2);
+        for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(corr[nb], neg, b[nb][0], b[nb][1]);
     }
+    const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
-        const float s0 = half_at(u.sc[0], t), s1 = half_at(u.sc[1], t);
+    for (int j = 0; j < 4; ++j) {
+        const float s0 = half_bits_to_float(sw[j], 0), s1 = half_bits_to_float(sw[j], 1);  // cols 16j+c, 16j+c+8
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            acc[mt][t][0] = fmaf(s0, g[mt][t][0] + corr[mt][0], acc[mt][t][0]);
-            acc[mt][t][1] = fmaf(s1, g[mt][t][1] + corr[mt][1], acc[mt][t][1]);
-            acc[mt][t][2] = fmaf(s0, g[mt][t][2] + corr[mt][2], acc[mt][t][2]);
-            acc[mt][t][3] = fmaf(s1, g[mt][t][3] + corr[mt][3], acc[mt][t][3]);
+        for (int nb = 0; nb < NB; ++nb) {
+            acc[j][nb][0] = fmaf(s0, g[j][nb][0] + corr[nb][0], acc[j][nb][0]);
+            acc[j][nb][1] = fmaf(s0, g[j][nb][1] + corr[nb][1], acc[j][nb][1]);
+            acc[j][nb][2] = fmaf(s1, g[j][nb][2] + corr[nb][0], acc[j][nb][2]);
+            acc[j][nb][3] = fmaf(s1, g[j][nb][3] + corr[nb][1], acc[j][nb][3]);
         }
     }
 }
 
-// grid = (cluster_k, n / (64*warps_n), ceil(m / (16*MT))), cluster = (cluster_k, 1, 1),
-// block = 32 * warps_n * warps_k.
-template <int MT, bool PF>
-__global__ void __launch_bounds__(MT == 1 ? 320 : 256) w4a16_decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    __nv_bfloat16 *sA = reinterpret_cast<__nv_bfloat16 *>(smem);
-    float *sRed = reinterpret_cast<float *>(smem + p.a_bytes);
+// grid = (cluster_k, n / (64*warps_n), ceil(m / (8*NB))), cluster = (cluster_k, 1, 1),
+// block = 32 * (1 + warps_n * warps_k): warp 0 produces, warp 1 + wk*warps_n + wn consumes
+// chunk wn of the stages i with i % warps_k == wk.
+template <int NB>
+__global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    uint8_t *base_gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sA = base, sRing = base + p.off_ring, sBar = base + p.off_bar;
+    float *sRed = reinterpret_cast<float *>(base_gen + p.off_red);
+    auto full = [&](int s) { return sBar + 8u * s; };
+    auto empty = [&](int s) { return sBar + 8u * (p.stages + s); };
+    const uint32_t a_full = sBar + 8u * (2 * p.stages);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(base_gen + p.off_bar + 8 * (2 * p.stages + 1));
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wn = warp % p.warps_n, wk = warp / p.warps_n;
-    const int chunk = blockIdx.y * p.warps_n + wn;
-    const int m0 = blockIdx.z * (16 * MT);
-    const int m_valid = min(16 * MT, p.m - m0);
+    constexpr int kRows = 8 * NB;
+    const int m0 = blockIdx.z * kRows;
+    const int m_valid = min(kRows, p.m - m0);
+    const int chunk0 = blockIdx.y * p.warps_n;
     const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
-
     const int gc0 = min(p.groups, static_cast<int>(rank) * p.groups_per_cta);
     const int gc1 = min(p.groups, gc0 + p.groups_per_cta);
+    const int nst = gc1 - gc0;  // stages this CTA streams
 
-    float acc[MT][8][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][t][i] = 0.f;
-
-    // lane-constant part of the ldmatrix address: row (lane%8) + 8*((lane/8)%2), column 8*(lane/16)
-    const uint32_t a_lane = smem_u32(sA) +
-                            2u * (static_cast<uint32_t>((lane & 7) + ((lane >> 3) & 1) * 8) * p.a_pitch +
-                                  static_cast<uint32_t>(lane >> 4) * 8);
-    const uint32_t a_mt_stride = 2u * 16u * p.a_pitch;
-
-    UnitRegs cur;
-    bool first_pass = true;
-    for (int pg0 = gc0; pg0 < gc1 || first_pass; pg0 += p.pass_groups) {
-        const int pg1 = min(gc1, pg0 + p.pass_groups);
-        const int plen = max(0, pg1 - pg0);
-        const int gpw = (plen + p.warps_k - 1) / p.warps_k;
-        const int g0 = min(pg1, pg0 + wk * gpw), g1 = min(pg1, g0 + gpw);
-
-        // weights never depend on the previous kernel: get them moving first
-        if (g0 < g1) load_unit(cur, p, g0, chunk, lane);
-        if (first_pass) {
-            pdl_launch_dependents();
-            pdl_wait();
-        } else {
-            __syncthreads();  // everyone is done reading the previous pass' activations
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), p.warps_n);
         }
-        // stage A[m0 .. m0+16MT, pg0*128 .. pg1*128) (zero rows past m)
-        {
-            const int vpr = plen * (kGroup / 8);  // 16-byte vectors per row
-            const int total = 16 * MT * vpr;
-            for (int v = tid; v < total; v += blockDim.x) {
-                const int row = v / vpr, cv = v - row * vpr;
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (row < m_valid)
-                    val = *reinterpret_cast<const uint4 *>(p.A + static_cast<size_t>(m0 + row) * p.k +
-                                                           static_cast<size_t>(pg0) * kGroup + cv * 8);
-                *reinterpret_cast<uint4 *>(sA + static_cast<size_t>(row) * p.a_pitch + cv * 8) = val;
-            }
-        }
-        __syncthreads();
-
-        for (int g = g0; g < g1; ++g) {
-            const uint32_t a_addr = a_lane + 2u * static_cast<uint32_t>(g - pg0) * kGroup;
-            if (PF) {
-                UnitRegs nxt;
-                const bool more = g + 1 < g1;
-                if (more) load_unit(nxt, p, g + 1, chunk, lane);
-                compute_unit<MT>(cur, a_addr, a_mt_stride, acc);
-                if (more) cur = nxt;
-            } else {
-                compute_unit<MT>(cur, a_addr, a_mt_stride, acc);
-                if (g + 1 < g1) load_unit(cur, p, g + 1, chunk, lane);
-            }
-        }
-        first_pass = false;
-    }
-
-    // ---- reduction over the K-warps of the CTA, then over the CTAs of the cluster ----------
-    {
-        const int c = lane >> 2, qd = lane & 3;
-        float *mine = sRed + static_cast<size_t>(wk) * (16 * MT) * p.red_pitch;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const int col = wn * 64 + 8 * t + 2 * qd;
-                const int r0 = mt * 16 + c;
-                if (r0 < m_valid)
-                    *reinterpret_cast<float2 *>(mine + r0 * p.red_pitch + col) =
-                        make_float2(acc[mt][t][0], acc[mt][t][1]);
-                if (r0 + 8 < m_valid)
-                    *reinterpret_cast<float2 *>(mine + (r0 + 8) * p.red_pitch + col) =
-                        make_float2(acc[mt][t][2], acc[mt][t][3]);
-            }
-        }
+        mbar_init(a_full, 1);
+        *abort_flag = 0;
+        mbar_init_fence();
     }
     __syncthreads();
+    pdl_launch_dependents();
+
+    const int nwarps_c = p.warps_n * p.warps_k;
+    float acc[4][NB][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[j][nb][i] = 0.f;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        const uint32_t w_row_bytes = static_cast<uint32_t>(p.warps_n) * 512u;
+        const uint32_t s_bytes = p.per_column ? 0u : static_cast<uint32_t>(p.warps_n) * 128u;
+        const uint32_t tx = 8u * w_row_bytes + s_bytes;
+        const size_t b_row_pitch = static_cast<size_t>(p.n) * 8;  // bytes per packed row (16 K)
+        bool ok = true;
+        auto issue_stage = [&](int i) {
+            const int s = i % p.stages;
+            const int g = gc0 + i;
+            const uint32_t dst = sRing + s * p.stage_bytes;
+            if (lane == 0) mbar_arrive_expect_tx(full(s), tx);
+            __syncwarp();
+            if (lane < 8)
+                bulk_g2s(dst + lane * w_row_bytes,
+                         p.B + (static_cast<size_t>(g) * 8 + lane) * b_row_pitch + static_cast<size_t>(chunk0) * 512,
+                         w_row_bytes, full(s));
+            else if (lane == 8 && s_bytes)
+                bulk_g2s(dst + 8 * w_row_bytes, p.S + static_cast<size_t>(g) * p.n + chunk0 * 64, s_bytes, full(s));
+        };
+        // weights never depend on the previous kernel: fill the ring first
+        const int pre = min(nst, p.stages);
+        for (int i = 0; i < pre; ++i) issue_stage(i);
+        pdl_wait();
+        // activations: one bulk copy per valid row, K range of this CTA
+        const uint32_t a_row_bytes = static_cast<uint32_t>(nst) * 256u;
+        if (nst > 0) {
+            if (lane == 0) mbar_arrive_expect_tx(a_full, a_row_bytes * m_valid);
+            __syncwarp();
+            for (int r = lane; r < m_valid; r += 32)
+                bulk_g2s(sA + r * p.a_pitch, p.A + static_cast<size_t>(m0 + r) * p.k + static_cast<size_t>(gc0) * kGroup,
+                         a_row_bytes, a_full);
+        }
+        for (int i = pre; i < nst && ok; ++i) {
+            const int s = i % p.stages;
+            const uint32_t ph = (i / p.stages) & 1;
+            ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x1100u | s);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) issue_stage(i);
+        }
+        if (!ok && lane == 0) {
+            // drain what was issued before leaving (shared memory must outlive the copies)
+            for (int i = max(0, nst - p.stages); i < nst; ++i) mbar_wait_quiet(full(i % p.stages), (i / p.stages) & 1);
+        }
+    } else if (warp <= nwarps_c) {
+        // ---------------- consumers ----------------
+        const int cw = warp - 1;
+        const int wn = cw % p.warps_n, wk = cw / p.warps_n;
+        const int qd = lane & 3, c = lane >> 2;
+        // lane-constant part of the ldmatrix address.  x2: lanes 0-7 rows 0-7 at K+0, lanes 8-15 the same
+        // rows at K+8.  x4 adds rows 8-15 for lanes 16-31.
+        const uint32_t a_lane = sA + static_cast<uint32_t>((lane & 7) + (NB == 2 ? (lane >> 4) * 8 : 0)) * p.a_pitch +
+                                static_cast<uint32_t>((lane >> 3) & 1) * 16u;
+        const uint32_t w_kt_stride = static_cast<uint32_t>(p.warps_n) * 512u;
+        bool ok = true;
+        if (wk < nst) ok = mbar_wait(a_full, 0, abort_flag, p.status, 0x1200u);
+        for (int i = wk; i < nst && ok; i += p.warps_k) {
+            const int s = i % p.stages;
+            const uint32_t ph = (i / p.stages) & 1;
+            if (!(ok = mbar_wait(full(s), ph, abort_flag, p.status, 0x1300u | s))) break;
+            const uint32_t st = sRing + s * p.stage_bytes;
+            if (!(p.debug & 1)) compute_stage<NB>(st + wn * 512u + lane * 16u, w_kt_stride, st + 8u * w_kt_stride + wn * 128u + 16u * c,
+                              !p.per_column, a_lane + static_cast<uint32_t>(i) * 256u, acc);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty(s));
+        }
+        // this warp's partial tile -> shared memory: acc[j][nb][i] is column 16j + c + 8*(i/2) of the chunk,
+        // batch row 8nb + 2qd + (i%2)
+        float *mine = sRed + static_cast<size_t>(wk) * kRows * p.red_pitch;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = 8 * nb + 2 * qd + (i & 1);
+                    if (row < m_valid) mine[row * p.red_pitch + wn * 64 + 16 * j + c + 8 * (i >> 1)] = acc[j][nb][i];
+                }
+    }
+    __syncthreads();
+
+    // ---- reduction over the K-teams of the CTA, then over the CTAs of the cluster -----------
     const int pairs_per_row = p.warps_n * 32;
     const int npairs = m_valid * pairs_per_row;
     if (p.warps_k > 1) {
@@ -223,8 +267,7 @@ __global__ void __launch_bounds__(MT == 1 ? 320 : 256) w4a16_decode_kernel(const
             float *dst = sRed + row * p.red_pitch + 2 * cp;
             float2 s = *reinterpret_cast<float2 *>(dst);
             for (int w = 1; w < p.warps_k; ++w) {
-                const float2 v =
-                    *reinterpret_cast<float2 *>(dst + static_cast<size_t>(w) * (16 * MT) * p.red_pitch);
+                const float2 v = *reinterpret_cast<float2 *>(dst + static_cast<size_t>(w) * kRows * p.red_pitch);
                 s.x += v.x;
                 s.y += v.y;
             }
@@ -234,15 +277,16 @@ __global__ void __launch_bounds__(MT == 1 ? 320 : 256) w4a16_decode_kernel(const
     }
     if (csize > 1) cluster_sync_all();
 
-    const int n0 = blockIdx.y * p.warps_n * 64;
+    pdl_wait();  // every thread that writes C orders itself after the previous kernel
+    const int n0 = chunk0 * 64;
     const int per_rank = (npairs + csize - 1) / csize;
     const int i0 = min(npairs, static_cast<int>(rank) * per_rank), i1 = min(npairs, i0 + per_rank);
-    const uint32_t red_base = smem_u32(sRed);
+    const uint32_t red_base = base + p.off_red;
     for (int idx = i0 + tid; idx < i1; idx += blockDim.x) {
         const int row = idx / pairs_per_row, cp = idx - row * pairs_per_row;
-        const uint32_t off = red_base + 4u * static_cast<uint32_t>(row * p.red_pitch + 2 * cp);
         float2 s;
         if (csize > 1) {
+            const uint32_t off = red_base + 4u * static_cast<uint32_t>(row * p.red_pitch + 2 * cp);
             s = make_float2(0.f, 0.f);
             for (uint32_t r = 0; r < csize; ++r) {
                 const float2 v = ld_dsmem_f2(map_to_cta(off, r));
@@ -267,76 +311,108 @@ __global__ void __launch_bounds__(MT == 1 ? 320 : 256) w4a16_decode_kernel(const
 
 // ---- host: decomposition heuristic and launch ---------------------------------------------
 
-namespace {
-
-constexpr int kPassCapMt1 = 10;  // groups of A staged at once (16 rows): 10*128*16*2 B = 40 KB
-constexpr int kPassCapMt2 = 5;
-
 struct DecodeConfig {
-    int mt, cluster_k, warps_k, warps_n, groups_per_cta, pass_groups;
-    bool prefetch;
+    int nb, cluster_k, warps_k, warps_n, groups_per_cta, stages;
 };
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Shared memory one CTA may use so that two CTAs (16 consumer warps) stay resident per SM.
+constexpr int kSmemBudget = 108 * 1024;
+
+int a_stage_bytes(int nb, int groups_per_cta) { return 8 * nb * (groups_per_cta * 256 + 16); }
+int red_bytes(int nb, int wk, int wn) { return 4 * wk * 8 * nb * (wn * 64 + 8); }
+
 DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
     DecodeConfig c{};
     const int groups = k / kGroup, chunks = n / kChunkCols;
-    c.mt = m <= 16 ? 1 : 2;
-    c.prefetch = c.mt == 1;
-    const int mblocks = ceil_div(m, 16 * c.mt);
+    c.nb = m <= 8 ? 1 : 2;
+    const int mblocks = ceil_div(m, 8 * c.nb);
     const int sms = device_sm_count();
-    const int max_warps = c.mt == 1 ? 10 : 8;
-
-    int wn = m <= 4 ? 1 : (m <= 8 ? 2 : 4);
-    int ck, wk;
+    int wn = 1, ck = 1, wk = 8;
     if (ov.cluster_k > 0 && ov.warps_k > 0 && ov.warps_n > 0) {
         ck = ov.cluster_k;
         wk = ov.warps_k;
         wn = ov.warps_n;
     } else {
-        // aim for about one resident wave: SMs x 12 warps (MT=1) or x 8 (MT=2)
-        const long long capacity = static_cast<long long>(sms) * (c.mt == 1 ? 12 : 8);
-        const long long units = static_cast<long long>(groups) * chunks * mblocks;
-        const int upw = static_cast<int>(units / capacity > 0 ? (units + capacity - 1) / capacity : 1);
-        const int kwarps = ceil_div(groups, upw);  // K-warps wanted per 64-column chunk
-        const int wk_cap = max_warps / wn > 0 ? max_warps / wn : 1;
-        ck = 1;
-        while (ck < 8 && ceil_div(kwarps, ck) > wk_cap) ck *= 2;
-        wk = ceil_div(kwarps, ck);
-        if (wk > wk_cap) wk = wk_cap;
-        if (wk < 1) wk = 1;
+        // Eight consumer warps per CTA (wn chunks x wk K-teams), two CTAs per SM.  Pick the chunk width
+        // and the cluster split whose grid fills one resident wave best and keeps every team busy.
+        double best = 1e30;
+        for (int twn = 1; twn <= 4; twn *= 2) {
+            if (chunks % twn) continue;
+            for (int tck = 1; tck <= 8; tck *= 2) {
+                if (tck > groups) continue;
+                const int twk = 8 / twn;
+                const int gpc = ceil_div(groups, tck);
+                if (a_stage_bytes(c.nb, gpc) + red_bytes(c.nb, twk, twn) + 2 * twn * 4224 > kSmemBudget) continue;
+                const long long ctas = static_cast<long long>(chunks / twn) * tck * mblocks;
+                const double waves = static_cast<double>((ctas + 2 * sms - 1) / (2 * sms));
+                const int per_team = ceil_div(gpc, twk);        // stages a team works through in sequence
+                const double fill = static_cast<double>(ctas) / (waves * 2 * sms);  // share of the wave in use
+                // time ~ waves * (fixed + sequential stages) ; wider clusters pay for the DSMEM reduction,
+                // narrow CTAs re-read the activations once per chunk
+                // narrow CTAs also mean 512-byte bulk copies, which the copy engine moves less efficiently
+                double t = waves * (3.0 + 1.0 * per_team) / (0.35 + 0.65 * fill) + 0.15 * tck +
+                           0.02 * m * (4.0 / twn) + (twn == 1 ? 2.0 : twn == 2 ? 0.4 : 0.0);
+                if (t < best) {
+                    best = t;
+                    wn = twn;
+                    ck = tck;
+                    wk = twk;
+                }
+            }
+        }
     }
     while (chunks % wn) wn /= 2;
     if (ck > 8) ck = 8;
-    if (ck > groups) ck = 1;
+    while (ck > groups) ck /= 2;
     c.cluster_k = ck;
     c.warps_k = wk;
     c.warps_n = wn;
     c.groups_per_cta = ceil_div(groups, ck);
-    const int cap = c.mt == 1 ? kPassCapMt1 : kPassCapMt2;
-    c.pass_groups = c.groups_per_cta < cap ? c.groups_per_cta : cap;
+    // Ring depth: whatever the per-CTA budget leaves.  When the CTA streams more stages than the ring
+    // holds, slots are reused, and then every slot must belong to exactly one K-team (depth a multiple
+    // of warps_k): a team that skipped a fill of a slot could not tell fills apart by barrier parity.
+    const int stage_bytes = wn * (8 * 512 + 128);
+    const int room = kSmemBudget - a_stage_bytes(c.nb, c.groups_per_cta) - red_bytes(c.nb, wk, wn) - 512;
+    int max_stages = room / stage_bytes;
+    if (max_stages > 16) max_stages = 16;
+    if (max_stages < 1) max_stages = 1;
+    if (c.groups_per_cta <= max_stages) {
+        c.stages = c.groups_per_cta;
+    } else {
+        if (wk > max_stages) wk = max_stages;
+        c.warps_k = wk;
+        c.stages = (max_stages / wk) * wk;
+    }
     return c;
 }
 
-template <int MT, bool PF>
-int launch_one(const DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t stream) {
+template <int NB>
+int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t stream) {
     static bool attr_set[64] = {};
-    const size_t smem = static_cast<size_t>(p.a_bytes) +
-                        sizeof(float) * static_cast<size_t>(c.warps_k) * 16 * MT * p.red_pitch;
+    constexpr int kMaxSmem = 200 * 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_decode_kernel<MT, PF>,
-                                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                            160 * 1024)))
+        if (int rc = record_cuda_error(
+                cudaFuncSetAttribute(w4a16_decode_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)))
             return rc;
         attr_set[dev] = true;
     }
-    if (smem > 160 * 1024) return KILN_W4A16_ERR_KERN_SHAPE;
+    // carve-up: [A rows][ring][reduction tiles][barriers]
+    auto align = [](int x, int a) { return (x + a - 1) / a * a; };
+    p.a_pitch = c.groups_per_cta * 256 + 16;
+    p.stage_bytes = c.warps_n * (8 * 512 + 128);
+    p.red_pitch = c.warps_n * 64 + 8;
+    p.off_ring = align(8 * NB * p.a_pitch, 128);
+    p.off_red = p.off_ring + align(c.stages * p.stage_bytes, 128);
+    p.off_bar = p.off_red + align(static_cast<int>(sizeof(float)) * c.warps_k * 8 * NB * p.red_pitch, 128);
+    const size_t smem = static_cast<size_t>(p.off_bar) + 8 * (2 * c.stages + 2) + 128;
+    if (smem > kMaxSmem) return KILN_W4A16_ERR_KERN_SHAPE;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(c.cluster_k, p.n / (kChunkCols * c.warps_n), (m + 16 * MT - 1) / (16 * MT));
-    cfg.blockDim = dim3(32 * c.warps_n * c.warps_k);
+    cfg.gridDim = dim3(c.cluster_k, p.n / (kChunkCols * c.warps_n), (m + 8 * NB - 1) / (8 * NB));
+    cfg.blockDim = dim3(32 * (1 + c.warps_n * c.warps_k));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
@@ -350,33 +426,42 @@ int launch_one(const DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t
     cfg.numAttrs = 2;
     if (cfg.gridDim.y > 65535 || cfg.gridDim.z > 65535) return KILN_W4A16_ERR_KERN_SHAPE;
     note_launch();
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_decode_kernel<MT, PF>, p));
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_decode_kernel<NB>, p));
 }
 
 }  // namespace
 
 int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
+    if (ov.cluster_k < 0) {  // A/B hook: the register-prefetch variant
+        DecodeOverride o2{-ov.cluster_k, ov.warps_k, ov.warps_n};
+        return launch_decode_regs(a, o2);
+    }
+    uint32_t *status = device_status_word();
+    if (!status) return KILN_W4A16_ERR_CUDA;
     const DecodeConfig c = choose_config(a.m, a.n, a.k, ov);
-    if (c.warps_n * c.warps_k * 32 > (c.mt == 1 ? 320 : 256)) return KILN_W4A16_ERR_KERN_SHAPE;
+    if ((1 + c.warps_n * c.warps_k) * 32 > 288) return KILN_W4A16_ERR_KERN_SHAPE;
+    if (c.stages < 1 || (c.groups_per_cta > c.stages && c.stages % c.warps_k != 0)) return KILN_W4A16_ERR_KERN_SHAPE;
+    // a CTA's K range must fit the activation stage: fall back to more cluster ranks is not possible
+    // past 8, so very long K runs go through the register variant, which stages K in passes
+    if (8 * c.nb * (c.groups_per_cta * 256 + 16) > 96 * 1024) return launch_decode_regs(a, DecodeOverride{0, 0, 0});
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16 *>(a.A);
-    p.B = static_cast<const uint4 *>(a.B);
+    p.B = static_cast<const uint8_t *>(a.B);
     p.S = static_cast<const __half *>(a.S);
     p.C = static_cast<__nv_bfloat16 *>(a.C);
+    p.status = status;
     p.m = a.m;
     p.n = a.n;
     p.k = a.k;
     p.groups = a.k / kGroup;
     p.groups_per_cta = c.groups_per_cta;
-    p.pass_groups = c.pass_groups;
     p.warps_n = c.warps_n;
     p.warps_k = c.warps_k;
+    p.stages = c.stages;
     p.per_column = a.groupsize == -1;
-    p.a_pitch = c.pass_groups * kGroup + 8;
-    p.red_pitch = c.warps_n * 64 + 8;
-    p.a_bytes = 16 * c.mt * p.a_pitch * 2;
-    if (c.mt == 1) return launch_one<1, true>(p, c, a.m, a.stream);
-    return launch_one<2, false>(p, c, a.m, a.stream);
+    { const char *e = getenv("KILN_W4A16_DEBUG"); p.debug = e ? atoi(e) : 0; }
+    if (c.nb == 1) return launch_one<1>(p, c, a.m, a.stream);
+    return launch_one<2>(p, c, a.m, a.stream);
 }
 
 }  // namespace kiln

@@ -23,7 +23,7 @@
 
 #include <mutex>
 
-#include "w4a16_common.cuh"
+#include "w4a16_async.cuh"
 
 namespace kiln {
 namespace {
@@ -34,7 +34,6 @@ constexpr int kNumThreads = 14 * 32;
 constexpr int kDequantWarp0 = 6;
 constexpr int kNumDequantThreads = 8 * 32;
 constexpr int kNumEpilogueThreads = 4 * 32;
-constexpr uint32_t kSpinLimit = 4u << 20;  // polls per wait; each poll may block ~a microsecond or more
 
 struct PrefillParams {
     const uint4 *B;
@@ -48,39 +47,6 @@ struct PrefillParams {
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait.  Returns false if the CTA is aborting (this wait or another one ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 63 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicCAS(status, 0u, code);
-    return false;
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -179,7 +145,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             mbar_init(tmem_empty(a), kNumEpilogueThreads);
         }
         *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -228,8 +194,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 for (uint32_t j = first; j < it; ++j) {
                     const int s = j % C::kStages;
                     const uint32_t ph = (j / C::kStages) & 1;
-                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(full_a(s), ph); ++i) {
-                    }
+                    mbar_wait_quiet(full_a(s), ph);
                 }
             }
         }

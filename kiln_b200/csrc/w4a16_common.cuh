@@ -122,6 +122,7 @@ int record_cuda_error(cudaError_t e);  // returns KILN_W4A16_ERR_CUDA if e != su
 uint32_t *device_status_word();        // per-device word written by bounded waits; nullptr on failure
 
 int launch_decode(const GemmArgs &a, const DecodeOverride &ov);
+int launch_decode_regs(const GemmArgs &a, const DecodeOverride &ov);
 int launch_prefill(const GemmArgs &a);
 size_t prefill_workspace_bytes(int m, int n, int k);
 bool prefill_supported(int m, int n, int k, int groupsize);

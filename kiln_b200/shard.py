@@ -1,0 +1,128 @@
+"""N-sharded column-parallel W4A16 GEMM across the GPUs of one node.
+
+The reference is single-GPU (its wrapper hard-codes device 0,
+kiln-marlin-gemm/src/lib.rs:210-215); this module is the multi-GPU extension of the same
+call.  Every output column depends on one column of the weight and its scales, and the
+Marlin layout is separable along N at 64-column granularity, so a shard is a plain slice
+of the packed tensors: b_packed[:, 2*n0:2*n1] and scales[:, n0:n1].  Rank r of g owns
+columns [r*N/g, (r+1)*N/g); activations are replicated; the one exchange step is an
+all-gather of the bf16 output slices (NCCL over NVLink on GPUs, any backend in tests).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .marlin_gemm import KilnMarlinError, marlin_w4a16_gemm
+from .marlin_proj import MarlinPackedProj
+
+
+def shard_bounds(n: int, rank: int, world: int) -> tuple:
+    """Column range [n0, n1) of `rank`; N/world must keep the kernel's 256-column rule."""
+    if world < 1 or not (0 <= rank < world):
+        raise KilnMarlinError(f"kiln-marlin-gemm: bad shard rank {rank} of {world}")
+    if n % world != 0 or (n // world) % 256 != 0:
+        raise KilnMarlinError(
+            f"kiln-marlin-gemm: n={n} cannot be split over {world} ranks in multiples of 256 columns")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_packed(b_packed: torch.Tensor, scales: torch.Tensor, rank: int, world: int):
+    """Slices of the packed weight [k/16, 2n] and the scales [k/g, n] owned by `rank` (contiguous copies)."""
+    n = scales.shape[1]
+    if b_packed.shape[1] != 2 * n:
+        raise KilnMarlinError(f"kiln-marlin-gemm: b_packed has {b_packed.shape[1]} columns, expected {2 * n}")
+    n0, n1 = shard_bounds(n, rank, world)
+    return b_packed[:, 2 * n0:2 * n1].contiguous(), scales[:, n0:n1].contiguous()
+
+
+def shard_proj(proj: MarlinPackedProj, rank: int, world: int) -> MarlinPackedProj:
+    b, s = shard_packed(proj.b_packed, proj.scales, rank, world)
+    return MarlinPackedProj(b, s, proj.groupsize, proj.k, proj.n // world)
+
+
+def all_gather_columns(local: torch.Tensor, group=None, out: Optional[torch.Tensor] = None,
+                       row_major: bool = False) -> torch.Tensor:
+    """All-gather of the [m, n/g] output slices.
+
+    Returns the blocked result [g, m, n/g] (block r = columns of rank r) -- what the collective
+    produces without another pass -- or, with row_major=True, the dense [m, n] matrix
+    (one extra device copy).  `out` may supply the blocked buffer.
+    """
+    world = dist.get_world_size(group)
+    m, nl = local.shape
+    if out is None:
+        out = torch.empty((world, m, nl), dtype=local.dtype, device=local.device)
+    elif tuple(out.shape) != (world, m, nl) or not out.is_contiguous():
+        raise KilnMarlinError("kiln-marlin-gemm: gather buffer must be contiguous [world, m, n/world]")
+    dist.all_gather_into_tensor(out.view(world * m, nl), local.contiguous(), group=group)
+    if row_major:
+        return out.permute(1, 0, 2).reshape(m, world * nl)
+    return out
+
+
+@dataclass
+class ColumnParallelLinear:
+    """One rank's shard of a W4A16 projection plus the gather of its outputs."""
+
+    shard: MarlinPackedProj
+    rank: int
+    world: int
+    group: object = None
+
+    @classmethod
+    def from_full(cls, proj: MarlinPackedProj, group=None) -> "ColumnParallelLinear":
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        return cls(shard_proj(proj, rank, world), rank, world, group)
+
+    def local(self, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return marlin_w4a16_gemm(a, self.shard.b_packed, self.shard.scales, self.shard.groupsize, out=out)
+
+    def forward(self, a: torch.Tensor, gathered: Optional[torch.Tensor] = None, row_major: bool = False,
+                m_chunks: int = 1) -> torch.Tensor:
+        """GEMM on the local columns, then all-gather.  With m_chunks > 1 the rows are processed in
+        chunks and each chunk's gather runs on a side stream while the next chunk's GEMM computes."""
+        if m_chunks <= 1 or not a.is_cuda:
+            return all_gather_columns(self.local(a), self.group, gathered, row_major)
+        m = a.shape[0]
+        nl = self.shard.n
+        if m % m_chunks != 0:
+            raise KilnMarlinError(f"kiln-marlin-gemm: m={m} not divisible by m_chunks={m_chunks}")
+        mc = m // m_chunks
+        # chunk-major blocked buffer [chunks, world, mc, nl]: each chunk's gather writes one contiguous slab
+        buf = torch.empty((m_chunks, self.world, mc, nl), dtype=torch.bfloat16, device=a.device)
+        local = torch.empty((m, nl), dtype=torch.bfloat16, device=a.device)
+        main = torch.cuda.current_stream(a.device)
+        side = _side_stream(a.device)
+        for c in range(m_chunks):
+            self.local(a[c * mc:(c + 1) * mc], out=local[c * mc:(c + 1) * mc])
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(ev)
+                dist.all_gather_into_tensor(buf[c].view(self.world * mc, nl), local[c * mc:(c + 1) * mc],
+                                            group=self.group)
+        main.wait_stream(side)
+        blocked = buf.permute(1, 0, 2, 3)  # [world, chunks, mc, nl] view
+        if row_major:
+            return blocked.permute(1, 2, 0, 3).reshape(m, self.world * nl)
+        out = blocked.reshape(self.world, m, nl)  # copies into the [g, m, n/g] layout
+        if gathered is not None:
+            gathered.copy_(out)
+            return gathered
+        return out
+
+
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    s = _side_streams.get(device)
+    if s is None:
+        s = torch.cuda.Stream(device)
+        _side_streams[device] = s
+    return s

@@ -1,0 +1,223 @@
+//! W4A16 GEMM for B200 behind the public API of kiln's `kiln-marlin-gemm` crate.
+//!
+//! Same two entry points as the crate it replaces: [`marlin_w4a16_gemm`] and [`pack`].
+//! Everything that computes lives under the C ABI of `include/kiln_w4a16.h`; this file only
+//! validates shapes the way the original wrapper does, borrows device pointers from candle
+//! and forwards them.  Differences from the original wrapper are all removals: no bf16<->fp16
+//! casts (the kernels read and write bf16), no zeroed lock buffer per call (split-K scratch is
+//! a cached per-device buffer, and the decode path needs none), no hard-coded device 0.
+//!
+//! NOTE: authored without a Rust toolchain at hand; it has not been compiled.
+
+use candle_core::{
+    backend::BackendStorage, cuda_backend::cudarc::driver::DevicePtr, DType, Result, Tensor,
+};
+use half::f16;
+use std::ffi::c_void;
+
+unsafe extern "C" {
+    fn kiln_w4a16_gemm_bf16(
+        a: *const c_void,
+        b: *const c_void,
+        c: *mut c_void,
+        s: *const c_void,
+        m: i32,
+        n: i32,
+        k: i32,
+        groupsize: i32,
+        workspace: *mut c_void,
+        workspace_bytes: usize,
+        stream: *mut c_void,
+    ) -> i32;
+    fn kiln_w4a16_workspace_bytes(m: i32, n: i32, k: i32) -> usize;
+    fn kiln_w4a16_quantize_and_pack_host(
+        weight: *const f32,
+        k: i32,
+        n: i32,
+        groupsize: i32,
+        b_packed: *mut i32,
+        scales_f16: *mut u16,
+        dequant: *mut f32,
+        num_threads: i32,
+    ) -> i32;
+    fn kiln_w4a16_build_weight_perm(out: *mut i32);
+    fn kiln_w4a16_build_scale_perm(out: *mut i32);
+    fn kiln_w4a16_build_scale_perm_single(out: *mut i32);
+}
+
+/// `a [m,k] bf16` x `b_packed [k/16, n*16/8] i32` x `scales [k/groupsize, n] f16` -> `[m,n] bf16`.
+/// Constraints and error messages follow the original wrapper.
+pub fn marlin_w4a16_gemm(
+    a: &Tensor,
+    b_packed: &Tensor,
+    scales: &Tensor,
+    groupsize: i32,
+) -> Result<Tensor> {
+    let device = a.device();
+    if !device.is_cuda() {
+        candle_core::bail!("kiln-marlin-gemm: a must be on CUDA");
+    }
+    let (m, k) = a.dims2()?;
+    let (b_rows, b_cols) = b_packed.dims2()?;
+    let (s_rows, n) = scales.dims2()?;
+    if k % 128 != 0 {
+        candle_core::bail!("kiln-marlin-gemm: k must be a multiple of 128 (got {k})");
+    }
+    if n % 256 != 0 {
+        candle_core::bail!("kiln-marlin-gemm: n must be a multiple of 256 (got {n})");
+    }
+    if b_rows != k / 16 || b_cols != n * 16 / 8 {
+        candle_core::bail!(
+            "kiln-marlin-gemm: b_packed shape [{b_rows}, {b_cols}] does not match expected \
+             [k/16={}, n*16/8={}] for k={k}, n={n}",
+            k / 16,
+            n * 16 / 8,
+        );
+    }
+    if !(groupsize == -1 || groupsize == 128) {
+        candle_core::bail!("kiln-marlin-gemm: groupsize must be -1 or 128 (got {groupsize})");
+    }
+    let g: usize = if groupsize == -1 { k } else { groupsize as usize };
+    if g > k || k % g != 0 {
+        candle_core::bail!("kiln-marlin-gemm: k={k} must be divisible by groupsize={groupsize}");
+    }
+    if s_rows != k / g {
+        candle_core::bail!(
+            "kiln-marlin-gemm: scales rows {s_rows} != expected {} (k={k}, groupsize={groupsize})",
+            k / g
+        );
+    }
+    if a.dtype() != DType::BF16 {
+        candle_core::bail!("kiln-marlin-gemm: a must be bf16 (got {:?})", a.dtype());
+    }
+    if b_packed.dtype() != DType::I32 {
+        candle_core::bail!("kiln-marlin-gemm: b_packed must be i32 (got {:?})", b_packed.dtype());
+    }
+    if scales.dtype() != DType::F16 {
+        candle_core::bail!("kiln-marlin-gemm: scales must be f16 (got {:?})", scales.dtype());
+    }
+
+    let a = a.contiguous()?;
+    let b_packed = b_packed.contiguous()?;
+    let scales = scales.contiguous()?;
+    // fully overwritten by the kernel; zeros() only because candle has no uninitialised constructor here
+    let c = Tensor::zeros((m, n), DType::BF16, device)?;
+    let ws_bytes = unsafe { kiln_w4a16_workspace_bytes(m as i32, n as i32, k as i32) };
+    let ws = Tensor::zeros((ws_bytes.max(16),), DType::U8, device)?;
+
+    {
+        let (a_st, a_l) = a.storage_and_layout();
+        let (b_st, b_l) = b_packed.storage_and_layout();
+        let (c_st, c_l) = c.storage_and_layout();
+        let (s_st, s_l) = scales.storage_and_layout();
+        let (w_st, w_l) = ws.storage_and_layout();
+        macro_rules! cuda {
+            ($st:expr, $what:literal) => {
+                match &*$st {
+                    candle_core::Storage::Cuda(c) => c,
+                    _ => candle_core::bail!(concat!("kiln-marlin-gemm: ", $what, " must be on CUDA")),
+                }
+            };
+        }
+        let (a_c, b_c, c_c, s_c, w_c) = (
+            cuda!(a_st, "a"),
+            cuda!(b_st, "b_packed"),
+            cuda!(c_st, "c"),
+            cuda!(s_st, "scales"),
+            cuda!(w_st, "workspace"),
+        );
+        let stream = a_c.device().cuda_stream();
+        let raw_stream = stream.cu_stream() as *mut c_void;
+        let a_s = a_c.as_cuda_slice::<half::bf16>()?.slice(a_l.start_offset()..);
+        let b_s = b_c.as_cuda_slice::<i32>()?.slice(b_l.start_offset()..);
+        let c_s = c_c.as_cuda_slice::<half::bf16>()?.slice(c_l.start_offset()..);
+        let s_s = s_c.as_cuda_slice::<f16>()?.slice(s_l.start_offset()..);
+        let w_s = w_c.as_cuda_slice::<u8>()?.slice(w_l.start_offset()..);
+        unsafe {
+            let (a_p, _g1) = a_s.device_ptr(&stream);
+            let (b_p, _g2) = b_s.device_ptr(&stream);
+            let (c_p, _g3) = c_s.device_ptr(&stream);
+            let (s_p, _g4) = s_s.device_ptr(&stream);
+            let (w_p, _g5) = w_s.device_ptr(&stream);
+            let status = kiln_w4a16_gemm_bf16(
+                a_p as *const _,
+                b_p as *const _,
+                c_p as *mut _,
+                s_p as *const _,
+                m as i32,
+                n as i32,
+                k as i32,
+                groupsize,
+                w_p as *mut _,
+                ws_bytes,
+                raw_stream,
+            );
+            if status != 0 {
+                candle_core::bail!(
+                    "kiln_marlin_w4a16_gemm failed with status {status} \
+                     (1=ERR_PROB_SHAPE, 2=ERR_KERN_SHAPE) for m={m}, n={n}, k={k}, \
+                     groupsize={groupsize}"
+                );
+            }
+        }
+    }
+    Ok(c)
+}
+
+/// Same surface as the original `pack` module; the work is done by the native packer.
+pub mod pack {
+    use super::*;
+
+    pub const MAX_Q: i32 = 15;
+    pub const Q_OFFSET: i32 = 8;
+
+    fn table(len: usize, f: unsafe extern "C" fn(*mut i32)) -> Vec<usize> {
+        let mut raw = vec![0i32; len];
+        unsafe { f(raw.as_mut_ptr()) };
+        raw.into_iter().map(|v| v as usize).collect()
+    }
+
+    pub fn build_weight_perm() -> Vec<usize> {
+        table(1024, kiln_w4a16_build_weight_perm)
+    }
+
+    pub fn build_scale_perm() -> Vec<usize> {
+        table(64, kiln_w4a16_build_scale_perm)
+    }
+
+    pub fn build_scale_perm_single() -> Vec<usize> {
+        table(32, kiln_w4a16_build_scale_perm_single)
+    }
+
+    /// `weight` row-major `[k, n]`; returns `(b_packed, scales, dequant)` exactly like the original.
+    /// Single-threaded per call (`num_threads = 1`): kiln already fans projections out over rayon.
+    pub fn quantize_and_pack(
+        weight: &[f32],
+        k: usize,
+        n: usize,
+        groupsize: i64,
+    ) -> (Vec<i32>, Vec<f16>, Vec<f32>) {
+        assert_eq!(weight.len(), k * n);
+        assert_eq!(k % 128, 0, "k must be %128 == 0");
+        assert_eq!(n % 256, 0, "n must be %256 == 0");
+        let g = if groupsize == -1 { k } else { groupsize as usize };
+        assert!(k % g == 0, "k={k} must be divisible by groupsize={g}");
+        let mut packed = vec![0i32; (k / 16) * (2 * n)];
+        let mut scales = vec![0u16; (k / g) * n];
+        let mut dequant = vec![0f32; k * n];
+        let rc = unsafe {
+            kiln_w4a16_quantize_and_pack_host(
+                weight.as_ptr(),
+                k as i32,
+                n as i32,
+                groupsize as i32,
+                packed.as_mut_ptr(),
+                scales.as_mut_ptr(),
+                dequant.as_mut_ptr(),
+                1,
+            )
+        };
+        assert_eq!(rc, 0, "kiln_w4a16_quantize_and_pack_host failed with status {rc}");
+        (packed, scales.into_iter().map(f16::from_bits).collect(), dequant)
+    }
+}

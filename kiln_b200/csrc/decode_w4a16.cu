@@ -335,33 +335,16 @@ DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
         wk = ov.warps_k;
         wn = ov.warps_n;
     } else {
-        // Eight consumer warps per CTA (wn chunks x wk K-teams), two CTAs per SM.  Pick the chunk width
-        // and the cluster split whose grid fills one resident wave best and keeps every team busy.
-        double best = 1e30;
-        for (int twn = 1; twn <= 4; twn *= 2) {
-            if (chunks % twn) continue;
-            for (int tck = 1; tck <= 8; tck *= 2) {
-                if (tck > groups) continue;
-                const int twk = 8 / twn;
-                const int gpc = ceil_div(groups, tck);
-                if (a_stage_bytes(c.nb, gpc) + red_bytes(c.nb, twk, twn) + 2 * twn * 4224 > kSmemBudget) continue;
-                const long long ctas = static_cast<long long>(chunks / twn) * tck * mblocks;
-                const double waves = static_cast<double>((ctas + 2 * sms - 1) / (2 * sms));
-                const int per_team = ceil_div(gpc, twk);        // stages a team works through in sequence
-                const double fill = static_cast<double>(ctas) / (waves * 2 * sms);  // share of the wave in use
-                // time ~ waves * (fixed + sequential stages) ; wider clusters pay for the DSMEM reduction,
-                // narrow CTAs re-read the activations once per chunk
-                // narrow CTAs also mean 512-byte bulk copies, which the copy engine moves less efficiently
-                double t = waves * (3.0 + 1.0 * per_team) / (0.35 + 0.65 * fill) + 0.15 * tck +
-                           0.02 * m * (4.0 / twn) + (twn == 1 ? 2.0 : twn == 2 ? 0.4 : 0.0);
-                if (t < best) {
-                    best = t;
-                    wn = twn;
-                    ck = tck;
-                    wk = twk;
-                }
-            }
-        }
+        // Rule fitted to sweeps over (cluster_k, warps_k, warps_n) on the Qwen3.5-4B projection shapes:
+        // two chunks per CTA (1 KB bulk copies, activations shared by two warps), the smallest cluster
+        // split that gives at least one CTA per SM while every CTA keeps two or more K groups, and
+        // four K-teams (two when a batch needs two MMAs per word and the registers that go with it).
+        wn = chunks % 2 == 0 ? 2 : 1;
+        ck = 1;
+        while (ck < 8 && static_cast<long long>(chunks / wn) * mblocks * ck < sms && groups / (ck * 2) >= 2) ck *= 2;
+        const int gpc = ceil_div(groups, ck);
+        wk = c.nb == 1 ? 4 : 2;
+        if (wk > gpc) wk = gpc;
     }
     while (chunks % wn) wn /= 2;
     if (ck > 8) ck = 8;

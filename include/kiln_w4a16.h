@@ -29,6 +29,7 @@ typedef int kiln_w4a16_status_t;
 #define KILN_W4A16_ERR_CUDA 5       /* a CUDA runtime/driver call failed (see kiln_w4a16_last_cuda_error) */
 #define KILN_W4A16_ERR_TIMEOUT 6    /* a bounded device-side wait gave up (read from the status word) */
 #define KILN_W4A16_ERR_ARG 7        /* null pointer / negative size / size above a stated maximum */
+#define KILN_W4A16_ERR_STATIC_SCRATCH 8 /* kiln_w4a16_gemm_bf16_noalloc: problem needs more than the built-in scratch */
 
 /* Replaces kiln_marlin_w4a16_gemm (crates/kiln-marlin-gemm/csrc/marlin_kernel.h:39-55,
  * crates/kiln-marlin-gemm/csrc/marlin_kernel.cu:831-860; Rust declaration
@@ -60,6 +61,27 @@ kiln_w4a16_status_t kiln_marlin_w4a16_gemm(const void *A, const void *B, void *C
 kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, const void *s, int m,
                                          int n, int k, int groupsize, void *workspace,
                                          size_t workspace_bytes, void *stream);
+
+/* No counterpart in the reference.  The same GEMM for callers that can neither allocate device
+ * memory when they call nor lend a workspace: a server whose start-up gave all remaining HBM to
+ * its KV-cache pool, or a serving loop that cannot take the device-wide synchronisation that
+ * cudaMalloc / cudaFree imply.  It always runs the tcgen05 kernel (whatever m is); where that kernel
+ * splits K, the fp32 partial sums go to a fixed array inside the library's device image instead of
+ * a caller buffer.  Limits and rules:
+ *   - the array is KILN_W4A16_NOALLOC_SCRATCH_BYTES (16 MiB) per GPU, held from library load to
+ *     process exit; a problem whose split needs more (splits * m * n * 4 bytes) is refused with
+ *     KILN_W4A16_ERR_STATIC_SCRATCH and nothing is launched;
+ *   - the call makes no cudaMalloc, cudaFree or other allocating call.  The first call on each
+ *     device looks up the array's device address (that device must be current) and sets the
+ *     kernel's shared-memory attribute; make that first call before any stream capture;
+ *   - every call on a GPU shares the one array, and it keeps the previous call's contents.
+ *     Nothing in it needs clearing (each split overwrites its slab before it is read), but two
+ *     calls that overlap on the same GPU (different streams) race on it: serialise them;
+ *   - bounded-wait failures of these launches are recorded in a status word of the same kind
+ *     inside the library image; kiln_w4a16_check_device_status does not read it. */
+#define KILN_W4A16_NOALLOC_SCRATCH_BYTES (16u << 20)
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const void *B, void *C, const void *s, int m,
+                                                 int n, int k, int groupsize, void *stream);
 
 /* Scratch bytes the GEMM needs for (m, n, k); replaces the reference wrapper's
  * fixed `(n/128) * 16` int32 lock array (crates/kiln-marlin-gemm/src/lib.rs:176-178). */

@@ -19,10 +19,11 @@ ERR_WORKSPACE = 4
 ERR_CUDA = 5
 ERR_TIMEOUT = 6
 ERR_ARG = 7
+ERR_STATIC_SCRATCH = 8
 
 STATUS_NAMES = {
     0: "OK", 1: "ERR_PROB_SHAPE", 2: "ERR_KERN_SHAPE", 3: "ERR_ALIGNMENT", 4: "ERR_WORKSPACE",
-    5: "ERR_CUDA", 6: "ERR_TIMEOUT", 7: "ERR_ARG",
+    5: "ERR_CUDA", 6: "ERR_TIMEOUT", 7: "ERR_ARG", 8: "ERR_STATIC_SCRATCH",
 }
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -31,6 +32,7 @@ _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 SIGNATURES = {
     "kiln_marlin_w4a16_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i]),
     "kiln_w4a16_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "kiln_w4a16_gemm_bf16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kiln_w4a16_workspace_bytes": (_sz, [_i, _i, _i]),
     "kiln_w4a16_shape_is_supported": (_i, [_i, _i]),
     "kiln_w4a16_build_weight_perm": (None, [_vp]),

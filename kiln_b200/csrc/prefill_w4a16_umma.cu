@@ -539,3 +539,108 @@ int launch_prefill(const GemmArgs &a) {
 }
 
 }  // namespace kiln
+
+// ---- the entry point that allocates nothing ---------------------------------------------------
+//
+// Some callers of this library cannot allocate device memory at call time and have no buffer to
+// lend either: an inference server that hands every remaining byte of HBM to its KV-cache pool at
+// start-up, or a serving loop that cannot afford the device-wide synchronisation a cudaMalloc or
+// cudaFree implies.  For them the split-K scratch of the prefill kernel lives in a fixed array in
+// the library's own device image.  Every GPU that loads the library holds these 16 MiB until the
+// process exits.
+namespace kiln {
+namespace {
+
+static __device__ __align__(256) float g_static_scratch[KILN_W4A16_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+static __device__ __align__(256) uint32_t g_static_status[64];
+
+struct StaticDeviceState {
+    float *scratch = nullptr;
+    uint32_t *status = nullptr;
+};
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the
+// address has to be asked for, once per device, with that device current.
+int static_state(StaticDeviceState **out) {
+    static StaticDeviceState per_device[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (int rc = record_cuda_error(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= 64) return KILN_W4A16_ERR_ARG;
+    std::lock_guard<std::mutex> lock(mu);
+    StaticDeviceState &st = per_device[dev];
+    if (!st.scratch) {
+        void *p_scratch = nullptr, *p_status = nullptr;
+        if (int rc = record_cuda_error(cudaGetSymbolAddress(&p_scratch, g_static_scratch))) return rc;
+        if (int rc = record_cuda_error(cudaGetSymbolAddress(&p_status, g_static_status))) return rc;
+        st.status = static_cast<uint32_t *>(p_status);
+        st.scratch = static_cast<float *>(p_scratch);
+    }
+    *out = &st;
+    return 0;
+}
+
+}  // namespace
+}  // namespace kiln
+
+extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const void *B, void *C, const void *s,
+                                                            int m, int n, int k, int groupsize, void *stream) {
+    using namespace kiln;
+    if (m < 0 || n < 0 || k < 0) return KILN_W4A16_ERR_ARG;
+    if (k % 128 != 0 || n % 256 != 0 || !(groupsize == -1 || groupsize == 128)) return KILN_W4A16_ERR_PROB_SHAPE;
+    if (m == 0 || n == 0 || k == 0) return KILN_W4A16_OK;
+    if (!A || !B || !C || !s) return KILN_W4A16_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C) |
+         reinterpret_cast<uintptr_t>(s)) & 15)
+        return KILN_W4A16_ERR_ALIGNMENT;
+    if (!prefill_supported(m, n, k, groupsize)) return KILN_W4A16_ERR_KERN_SHAPE;
+
+    const PrefillConfig c = choose_prefill(m, n, k);
+    const size_t need = c.splits > 1 ? static_cast<size_t>(c.splits) * m * n * sizeof(float) : 0;
+    if (need > KILN_W4A16_NOALLOC_SCRATCH_BYTES) return KILN_W4A16_ERR_STATIC_SCRATCH;
+
+    StaticDeviceState *st = nullptr;
+    if (int rc = static_state(&st)) return rc;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return KILN_W4A16_ERR_CUDA;
+
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(A), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return KILN_W4A16_ERR_CUDA;
+
+    PrefillParams p{};
+    p.B = static_cast<const uint4 *>(B);
+    p.S = static_cast<const __half *>(s);
+    p.C = static_cast<__nv_bfloat16 *>(C);
+    // Nothing in the scratch has to start at zero: every split writes its whole [m, n] slab before the
+    // reduction reads it, so what the previous call left behind is simply overwritten.
+    p.partial = st->scratch;
+    p.status = st->status;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.m_tiles = (m + BM - 1) / BM;
+    p.n_tiles = n / c.bn;
+    p.splits = c.splits;
+    p.k_iters = k / BK;
+    p.per_column = groupsize == -1;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    int rc = c.bn == 256 ? launch_bn<256>(tmap, p, cs) : launch_bn<128>(tmap, p, cs);
+    if (rc) return rc;
+    if (c.splits > 1) {
+        const size_t total4 = static_cast<size_t>(m) * n / 4;
+        int blocks = static_cast<int>((total4 + 255) / 256);
+        const int cap = device_sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        note_launch();
+        splitk_reduce_kernel<<<blocks, 256, 0, cs>>>(p.partial, p.C, p.S, m, n, c.splits, p.per_column);
+        rc = record_cuda_error(cudaGetLastError());
+    }
+    return rc;
+}

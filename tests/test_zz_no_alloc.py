@@ -1,0 +1,86 @@
+"""The entry point that allocates nothing: kiln_w4a16_gemm_bf16_noalloc.
+
+Who needs it: a caller that cannot allocate device memory when it calls and has no workspace to lend
+either -- for example a server that gave all remaining HBM to its KV-cache pool at start-up, or a
+serving loop that cannot take the device-wide synchronisation of cudaMalloc/cudaFree.  The split-K
+scratch of the tcgen05 kernel then lives in a 16 MiB array inside the library's device image.
+
+The test calls it through the C ABI twice in a row on shapes where the kernel really splits K (so the
+built-in scratch is used, and the second call finds the first call's leftovers in it) and compares with
+the regular entry point, which takes the scratch from the caller.  Both run the same kernel with the
+same split, so the outputs must be identical; the oracle tolerance (1e-2 of max) is checked as well.
+This file sorts last so that a run that stops at the first failure has already run everything else."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import kiln_b200
+from kiln_b200 import _lib
+import oracle
+from oracle import C
+from tests.util import REL_TOL, from_torch_bf16, rel_err, to_torch_bf16
+
+pytestmark = pytest.mark.gpu
+
+SCRATCH_LIMIT = 16 << 20
+
+
+def _case(m, k, n, seed, device):
+    a, q, s = oracle.synth_inputs(m, k, n, seed=seed)
+    packed, sp = kiln_b200.pack.repack(q, s, 128)
+    return dict(a=a, q=q, s=s, a_t=to_torch_bf16(a, device), b_t=torch.from_numpy(packed).to(device),
+                s_t=torch.from_numpy(sp.view(np.int16).copy()).view(torch.float16).to(device))
+
+
+def _noalloc(case, m, k, n):
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=case["a_t"].device)
+    rc = _lib.lib().kiln_w4a16_gemm_bf16_noalloc(case["a_t"].data_ptr(), case["b_t"].data_ptr(), out.data_ptr(),
+                                                 case["s_t"].data_ptr(), m, n, k, 128,
+                                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.STATUS_NAMES.get(rc, rc)
+    return out
+
+
+def test_noalloc_entry_matches_regular_entry_twice_in_a_row(cuda_device):
+    lib = _lib.lib()
+    shapes = [(256, 9216, 2560), (384, 9216, 512)]  # both split K: the scratch is really used
+    for m, k, n in shapes:
+        need = lib.kiln_w4a16_workspace_bytes(m, n, k)
+        assert 0 < need <= SCRATCH_LIMIT, "test shape must use split-K scratch within the built-in limit"
+    cases = [(_case(m, k, n, 900 + i, cuda_device), m, k, n) for i, (m, k, n) in enumerate(shapes)]
+    # two calls in a row, different problems: the second finds the first one's partial sums in the array
+    outs = [_noalloc(c, m, k, n) for c, m, k, n in cases]
+    outs2 = [_noalloc(c, m, k, n) for c, m, k, n in cases]
+    torch.cuda.synchronize()
+    for (c, m, k, n), o1, o2 in zip(cases, outs, outs2):
+        ref_entry = kiln_b200.marlin_w4a16_gemm(c["a_t"], c["b_t"], c["s_t"], 128)  # caller-owned workspace
+        torch.cuda.synchronize()
+        assert not torch.isnan(o1.float()).any()
+        assert torch.equal(o1, ref_entry) and torch.equal(o2, ref_entry)
+        rows = np.array([0, 1, m // 2, m - 1])
+        ref = C.gemm_fp64(c["a"][rows], c["q"], c["s"], 128)
+        assert rel_err(from_torch_bf16(o2[torch.from_numpy(rows).to(o2.device)]), ref) <= REL_TOL
+
+
+def test_noalloc_entry_small_m_and_no_split(cuda_device):
+    # any m goes through the tcgen05 kernel here; a shape that does not split K uses no scratch at all
+    for m, k, n in [(5, 256, 512), (130, 512, 768)]:
+        c = _case(m, k, n, 950 + m, cuda_device)
+        out = _noalloc(c, m, k, n)
+        torch.cuda.synchronize()
+        ref = C.gemm_fp64(c["a"], c["q"], c["s"], 128)
+        assert rel_err(from_torch_bf16(out), ref) <= REL_TOL
+
+
+def test_noalloc_entry_rejects_what_does_not_fit(cuda_device):
+    lib = _lib.lib()
+    m, k, n = 384, 16384, 4096  # its split needs 18 MiB
+    assert lib.kiln_w4a16_workspace_bytes(m, n, k) > SCRATCH_LIMIT
+    p = ctypes.c_void_p(0x1000)
+    before = lib.kiln_w4a16_launch_count()
+    assert lib.kiln_w4a16_gemm_bf16_noalloc(p, p, p, p, m, n, k, 128, None) == _lib.ERR_STATIC_SCRATCH
+    assert lib.kiln_w4a16_launch_count() == before  # refused before anything was launched
+    assert lib.kiln_w4a16_gemm_bf16_noalloc(p, p, p, p, 4, 200, 128, 128, None) == _lib.ERR_PROB_SHAPE
+    assert lib.kiln_w4a16_gemm_bf16_noalloc(None, p, p, p, 4, 256, 128, 128, None) == _lib.ERR_ARG

@@ -303,9 +303,20 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     d.w[b] = ld_stream_v4(p.B + idx);
                 }
             };
-            DequantRegs r0, r1;
+            auto load_scales = [&](int g) {
+                return ld_stream_v4(reinterpret_cast<const uint4 *>(
+                    p.S + static_cast<size_t>(g) * p.n + (nt * kChunksPerTile + dw % kChunksPerTile) * 64 + 8 * c));
+            };
+            uint4 sv_next = make_uint4(0, 0, 0, 0);
+            int next_group = -1;
+            if (!p.per_column) {
+                next_group = ki0 >> 1;
+                sv_next = load_scales(next_group);
+            }
+            DequantRegs r0, r1, r2;  // packed words of K-steps ki, ki+1, ki+2: three L2 round trips in flight
             load_regs(r0, ki0);
             if (ki0 + 1 < ki1) load_regs(r1, ki0 + 1);
+            if (ki0 + 2 < ki1) load_regs(r2, ki0 + 2);
             for (int ki = ki0; ki < ki1; ++ki, ++it) {
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1;
@@ -317,9 +328,12 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
 #pragma unroll
                         for (int t = 0; t < 8; ++t) s2[t] = 0x3F803F80u;  // bf16x2 {1, 1}; scale applied in the epilogue
                     } else {
-                        const int ch = dw % kChunksPerTile;
-                        const uint4 sv = ld_stream_v4(reinterpret_cast<const uint4 *>(
-                            p.S + static_cast<size_t>(g) * p.n + (nt * kChunksPerTile + ch) * 64 + 8 * c));
+                        // the scales of this group were requested when the previous group started
+                        const uint4 sv = (next_group == g) ? sv_next : load_scales(g);
+                        if (g + 1 <= ((ki1 - 1) >> 1)) {
+                            sv_next = load_scales(g + 1);
+                            next_group = g + 1;
+                        }
                         const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
                         for (int t = 0; t < 8; ++t) {
@@ -368,7 +382,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 fence_proxy_async_smem();
                 mbar_arrive(full_b(s));
                 r0 = r1;
-                if (ki + 2 < ki1) load_regs(r1, ki + 2);
+                r1 = r2;
+                if (ki + 3 < ki1) load_regs(r2, ki + 3);
             }
         }
     }

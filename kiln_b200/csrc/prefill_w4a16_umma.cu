@@ -95,10 +95,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
-template <int BN>
+// MT = M-tiles of 128 rows that share one dequantised B stage.  With MT = 2 every weight is dequantised
+// once per 256 rows instead of once per 128, which halves the dequant work per MMA flop; the two
+// accumulators then take both TMEM buffers, so the epilogue only partly overlaps the next tile.
+template <int BN, int MT = 1>
 struct Cfg {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
-    static constexpr int kABytes = BM * BK * 2;  // 16 KB
+    static constexpr int kABytes = MT * BM * BK * 2;  // 16 KB per M-tile
+    static constexpr int kStages = (192 * 1024) / (kABytes + BN * BK * 2);
     static constexpr int kBBytes = BN * BK * 2;  // 32 / 16 KB
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
@@ -115,10 +118,10 @@ struct DequantRegs {
     uint4 w[2];
 };
 
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, MT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -185,7 +188,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x100u | s))) break;
                     mbar_arrive_expect_tx(full_a(s), C::kABytes);
-                    tma_load_2d(smem_base + s * C::kStageBytes, &tmap_a, ki * BK, mt * BM, full_a(s));
+                    tma_load_2d(smem_base + s * C::kStageBytes, &tmap_a, ki * BK, mt * (BM * MT), full_a(s));
                 }
             }
             if (!ok) {
@@ -206,24 +209,32 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
                 int mt, nt, sp, ki0, ki1;
                 decode_unit(u, mt, nt, sp, ki0, ki1);
-                const uint32_t acc = tile & 1, acc_ph = (tile >> 1) & 1;
-                if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc))) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                // MT == 1: the two TMEM buffers alternate between tiles.  MT == 2: buffer h holds M-tile h of the pair.
+                const uint32_t acc0 = MT == 1 ? (tile & 1) : 0u, acc_ph = MT == 1 ? ((tile >> 1) & 1) : (tile & 1);
                 for (int ki = ki0; ki < ki1; ++ki, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s))) break;
                     if (!(ok = mbar_wait(full_b(s), ph, abort_flag, p.status, 0x400u | s))) break;
                     tc_fence_after();
-                    const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes);
                     const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes);
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)
-                        umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, C::kIdesc, (ki > ki0 || kk > 0) ? 1u : 0u);
+                    for (int h = 0; h < MT; ++h) {
+                        const uint32_t acc = acc0 + h;
+                        if (ki == ki0) {  // first write into this accumulator: the epilogue must have drained it
+                            if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc))) break;
+                            tc_fence_after();
+                        }
+                        const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes + h * (BM * BK * 2));
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk)
+                            umma_bf16(tmem_base + acc * BN, a_desc + 2 * kk, b_desc + 2 * kk, C::kIdesc,
+                                      (ki > ki0 || kk > 0) ? 1u : 0u);
+                        if (ki == ki1 - 1) umma_commit(tmem_full(acc));  // accumulator h is complete
+                    }
+                    if (!ok) break;
                     umma_commit(empty(s));  // frees the stage when these MMAs have read it
                 }
-                if (ok) umma_commit(tmem_full(acc));
             }
         }
     } else if (warp < kDequantWarp0) {
@@ -234,10 +245,13 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
         for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
             int mt, nt, sp, ki0, ki1;
             decode_unit(u, mt, nt, sp, ki0, ki1);
-            const uint32_t acc = tile & 1, acc_ph = (tile >> 1) & 1;
+            const uint32_t acc0 = MT == 1 ? (tile & 1) : 0u, acc_ph = MT == 1 ? ((tile >> 1) & 1) : (tile & 1);
+#pragma unroll 1
+            for (int h = 0; h < MT && ok; ++h) {
+            const uint32_t acc = acc0 + h;
             if (!(ok = mbar_wait(tmem_full(acc), acc_ph, abort_flag, p.status, 0x500u | acc))) break;
             tc_fence_after();
-            const int row = mt * BM + quarter * 32 + lane;
+            const int row = (mt * MT + h) * BM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
@@ -279,6 +293,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             }
             tc_fence_before();
             mbar_arrive(tmem_empty(acc));
+            }
         }
     } else {
         // ---------------- dequant: packed int4 -> bf16 B tile ----------------
@@ -430,30 +445,42 @@ __global__ void splitk_reduce_kernel(const float *partial, __nv_bfloat16 *C, con
 // ---- host -----------------------------------------------------------------------------------
 
 struct PrefillConfig {
-    int bn, splits;
+    int bn, splits, mt;
 };
 
-PrefillConfig choose_prefill(int m, int n, int k) {
+// Microseconds per 64-K step of one CTA, from measurements on B200: the dequant warps need about
+// 0.70 us for a 256-column B stage (0.37 us for 128 columns); the MMAs of one M-tile against it need
+// about 0.27 us (0.14 us).  A step costs whichever is longer.
+double step_us(int bn, int mt) {
+    const double dequant = bn == 256 ? 0.70 : 0.37, mma = (bn == 256 ? 0.27 : 0.14) * mt;
+    return dequant > mma ? dequant : mma;
+}
+
+PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
     const int sms = device_sm_count();
-    const int m_tiles = (m + BM - 1) / BM, k_iters = k / BK;
-    PrefillConfig best{256, 1};
+    const int k_iters = k / BK;
+    PrefillConfig best{256, 1, 1};
     double best_t = 1e30;
     const int bns[2] = {256, 128};
     const int ss[6] = {1, 2, 3, 4, 6, 8};
-    for (int bi = 0; bi < 2; ++bi)
-        for (int si = 0; si < 6; ++si) {
-            const int bn = bns[bi], s = ss[si];
-            if (k_iters / s < 8) continue;
-            const long long units = static_cast<long long>(m_tiles) * (n / bn) * s;
-            const double waves = static_cast<double>((units + sms - 1) / sms);
-            const double t_iter = bn == 256 ? 0.40 : 0.23;  // microseconds per 64-K step, measured order of magnitude
-            double t = waves * (static_cast<double>(k_iters) / s * t_iter + 0.3) + 1.5;
-            if (s > 1) t += 3.0 + (static_cast<double>(s) + 0.5) * m * static_cast<double>(n) * 4.0 * 2.0 / 4.0e6;
-            if (t < best_t) {
-                best_t = t;
-                best = PrefillConfig{bn, s};
+    for (int mt = 1; mt <= (allow_pairs ? 2 : 1); ++mt)
+        for (int bi = 0; bi < 2; ++bi)
+            for (int si = 0; si < 6; ++si) {
+                const int bn = bns[bi], s = ss[si];
+                if (k_iters / s < 8) continue;
+                if (mt == 2 && m <= BM) continue;
+                const int m_tiles = (m + BM * mt - 1) / (BM * mt);
+                const long long units = static_cast<long long>(m_tiles) * (n / bn) * s;
+                const double waves = static_cast<double>((units + sms - 1) / sms);
+                // the epilogue of a pair is only half hidden behind the next tile
+                const double epi = mt == 2 ? (bn == 256 ? 1.5 : 0.8) : 0.3;
+                double t = waves * (static_cast<double>(k_iters) / s * step_us(bn, mt) + epi) + 1.5;
+                if (s > 1) t += 3.0 + (static_cast<double>(s) + 0.5) * m * static_cast<double>(n) * 4.0 * 2.0 / 4.0e6;
+                if (t < best_t) {
+                    best_t = t;
+                    best = PrefillConfig{bn, s, mt};
+                }
             }
-        }
     return best;
 }
 
@@ -474,14 +501,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BN>
+template <int BN, int MT = 1>
 int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stream) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, MT>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN>,
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT>,
                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
             return rc;
         attr_set[dev] = true;
@@ -489,7 +516,7 @@ int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stre
     const int units = p.m_tiles * p.n_tiles * p.splits;
     const int grid = units < device_sm_count() ? units : device_sm_count();
     note_launch();
-    w4a16_prefill_kernel<BN><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, p);
+    w4a16_prefill_kernel<BN, MT><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, p);
     return record_cuda_error(cudaGetLastError());
 }
 
@@ -515,7 +542,7 @@ int launch_prefill(const GemmArgs &a) {
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k) * 2};
-    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(BM * c.mt)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.A), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -531,7 +558,7 @@ int launch_prefill(const GemmArgs &a) {
     p.m = a.m;
     p.n = a.n;
     p.k = a.k;
-    p.m_tiles = (a.m + BM - 1) / BM;
+    p.m_tiles = (a.m + BM * c.mt - 1) / (BM * c.mt);
     p.n_tiles = a.n / c.bn;
     p.splits = c.splits;
     p.k_iters = a.k / BK;
@@ -539,7 +566,11 @@ int launch_prefill(const GemmArgs &a) {
     if (c.splits > 1 && (!a.workspace || a.workspace_bytes < static_cast<size_t>(c.splits) * a.m * a.n * sizeof(float)))
         return KILN_W4A16_ERR_WORKSPACE;
 
-    int rc = c.bn == 256 ? launch_bn<256>(tmap, p, a.stream) : launch_bn<128>(tmap, p, a.stream);
+    int rc;
+    if (c.mt == 2)
+        rc = c.bn == 256 ? launch_bn<256, 2>(tmap, p, a.stream) : launch_bn<128, 2>(tmap, p, a.stream);
+    else
+        rc = c.bn == 256 ? launch_bn<256, 1>(tmap, p, a.stream) : launch_bn<128, 1>(tmap, p, a.stream);
     if (rc) return rc;
     if (c.splits > 1) {
         const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;
@@ -610,7 +641,7 @@ extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const
         return KILN_W4A16_ERR_ALIGNMENT;
     if (!prefill_supported(m, n, k, groupsize)) return KILN_W4A16_ERR_KERN_SHAPE;
 
-    const PrefillConfig c = choose_prefill(m, n, k);
+    const PrefillConfig c = choose_prefill(m, n, k, /*allow_pairs=*/false);
     const size_t need = c.splits > 1 ? static_cast<size_t>(c.splits) * m * n * sizeof(float) : 0;
     if (need > KILN_W4A16_NOALLOC_SCRATCH_BYTES) return KILN_W4A16_ERR_STATIC_SCRATCH;
 

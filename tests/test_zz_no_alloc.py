@@ -7,8 +7,9 @@ scratch of the tcgen05 kernel then lives in a 16 MiB array inside the library's 
 
 The test calls it through the C ABI twice in a row on shapes where the kernel really splits K (so the
 built-in scratch is used, and the second call finds the first call's leftovers in it) and compares with
-the regular entry point, which takes the scratch from the caller.  Both run the same kernel with the
-same split, so the outputs must be identical; the oracle tolerance (1e-2 of max) is checked as well.
+the regular entry point, which takes the scratch from the caller, within the tolerance all GEMM tests use
+(1e-2 of the largest output; the two entry points may pick different tilings, so the fp32 summation order
+can differ).  The two calls of the new entry point itself must agree bit for bit, and the oracle is checked too.
 This file sorts last so that a run that stops at the first failure has already run everything else."""
 import ctypes
 
@@ -58,7 +59,9 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row(cuda_device):
         ref_entry = kiln_b200.marlin_w4a16_gemm(c["a_t"], c["b_t"], c["s_t"], 128)  # caller-owned workspace
         torch.cuda.synchronize()
         assert not torch.isnan(o1.float()).any()
-        assert torch.equal(o1, ref_entry) and torch.equal(o2, ref_entry)
+        assert torch.equal(o1, o2), "second call (scratch holding the first call's partial sums) changed the result"
+        d = float((o1.float() - ref_entry.float()).abs().max() / ref_entry.float().abs().max())
+        assert d <= REL_TOL, f"no-alloc entry differs from the regular entry by {d}"
         rows = np.array([0, 1, m // 2, m - 1])
         ref = C.gemm_fp64(c["a"][rows], c["q"], c["s"], 128)
         assert rel_err(from_torch_bf16(o2[torch.from_numpy(rows).to(o2.device)]), ref) <= REL_TOL

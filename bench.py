@@ -285,6 +285,53 @@ def prefill_detail(d: Device, peaks):
     return out
 
 
+def sharded_detail(d: Device, world: int, rank: int):
+    """The path's N-sharded configuration: M=16384, K=9216, N=73728 split by columns over the ranks, local
+    GEMM + NCCL all-gather of the bf16 slices (blocked [g, M, N/g] result).  Times are max over ranks."""
+    import torch.distributed as dist
+
+    t = d.torch
+    m, k, n = 16384, 9216, 73728
+    nl = n // world
+    w = d.weights(k, nl, 1)[0]
+    a = d.acts(m, k)
+    local = t.empty((m, nl), dtype=t.bfloat16, device=d.dev)
+    gathered = t.empty((world, m, nl), dtype=t.bfloat16, device=d.dev) if world > 1 else None
+    from kiln_b200.shard import all_gather_columns
+
+    def once():
+        e = [t.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        d.gemm(a, w, local)
+        e[1].record()
+        if world > 1:
+            all_gather_columns(local, None, gathered)
+        e[2].record()
+        t.cuda.synchronize()
+        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[0].elapsed_time(e[2])
+
+    once()
+    once()
+    if world > 1:
+        dist.barrier()
+    reps = [once() for _ in range(3)]
+    med = [sorted(x[i] for x in reps)[1] for i in range(3)]
+    if world > 1:
+        tt = t.tensor(med, device=d.dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        med = [float(v) for v in tt.tolist()]
+    flops = alg_flops(m, k, n)
+    out = {
+        "m": m, "k": k, "n": n, "n_per_gpu": nl, "gemm_ms": round(med[0], 3), "allgather_ms": round(med[1], 3),
+        "total_ms": round(med[2], 3), "TFLOPs_per_gpu_gemm": round(flops / world / med[0] / 1e9, 1),
+        "TFLOPs_total_end_to_end": round(flops / med[2] / 1e9, 1),
+        "allgather_GBps_per_gpu_recv": round((world - 1) * m * nl * 2 / med[1] / 1e6, 1) if world > 1 else None,
+        "layout": "blocked [g, M, N/g]", "scaling": "strong",
+    }
+    del w, a, local, gathered
+    return out
+
+
 def run_only(args):
     """One shape with plain (non-graph) launches over rotating weights: the command ncu profiles."""
     kind, name, m = args.only.split(":")
@@ -449,6 +496,10 @@ def run_ours(args):
                 "ms_per_step": ct * 1e3,
                 "sample": f"{reps} passes of the full 32-GEMM sweep on the host (dequantise to bf16, f32 matmul)",
             }
+    if not args.quick:
+        sh = sharded_detail(d, world, rank)  # every rank takes part (collective inside)
+        if rank == 0:
+            line["sharded"] = sh
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libkiln_w4a16.so")
+# KILN_W4A16_LIB may point at another build of the same library (same C ABI)
+LIB_PATH = os.environ.get("KILN_W4A16_LIB") or os.path.join(_HERE, "libkiln_w4a16.so")
 
 OK = 0
 ERR_PROB_SHAPE = 1

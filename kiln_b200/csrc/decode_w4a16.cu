@@ -11,8 +11,7 @@
 //    weight stream starts before the previous kernel in the stream has finished
 //    (programmatic dependent launch; only the activations wait for it).
 //  * consumer warps: in-register int4 -> bf16 dequant (`lop3` puts each nibble pair into the
-//    mantissa of bf16x2 {128,128}; the shifts that align the nibbles are issued as high
-//    multiplies so they run beside the `lop3`s on another pipe); the +128+8 offset is not
+//    mantissa of bf16x2 {128,128}); the +128+8 offset is not
 //    subtracted per weight but removed per MMA tile by one extra MMA against a constant
 //    -136 fragment; bf16 m16n8k16 tensor-core MMAs with fp32 accumulation; the fp16 group
 //    scale is applied once per 128-K group to the fp32 partial sums (exact scale).
@@ -42,7 +41,7 @@ struct DecodeParams {
     int a_pitch;         // bytes per staged activation row (groups_per_cta*256 + 16)
     int red_pitch;       // floats per reduction row (warps_n*64 + 8)
     // shared-memory carve-up (bytes from the 128-byte aligned base)
-    int off_ring, off_red, off_bar, stage_bytes;
+    int off_ring, off_red, off_recv, off_bar, stage_bytes;
     int debug;  // bit0: skip compute, bit1: skip reduce
 };
 
@@ -56,10 +55,11 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
     return v;
 }
 
-// x >> s as a high multiply (runs on the FMA pipe, beside the lop3s on the ALU pipe)
+// Nibble alignment shift.  Measured on B200: plain ALU shifts beat high multiplies on the FMA pipe here
+// (gate+up M=1 11.6 us vs 12.7 us; IMAD.HI issues at a quarter of the rate), so the shifts stay on the ALU.
 template <int S>
 __device__ __forceinline__ uint32_t shr_mul(uint32_t x) {
-    return __umulhi(x, 1u << (32 - S));
+    return x >> S;
 }
 
 // One stage for one warp: 8 K-tiles of one 64-column chunk.
@@ -107,10 +107,17 @@ __device__ __forceinline__ void compute_stage(uint32_t w_addr, uint32_t w_kt_str
         for (int j = 0; j < 4; ++j) {
             const uint32_t x = xs[j];
             uint32_t f[4];
+#if defined(KILN_DECODE_NODEQ)
+            f[0] = x; f[1] = x; f[2] = x; f[3] = x;
+#elif defined(KILN_DECODE_NOSHIFT)
+            f[0] = lop3_and_or(x, kNibMask, kMagic128); f[1] = lop3_and_or(x, 0x00F000F0u, kMagic128);
+            f[2] = lop3_and_or(x, 0x0F000F00u, kMagic128); f[3] = lop3_and_or(x, 0xF000F000u, kMagic128);
+#else
             f[0] = lop3_and_or(x, kNibMask, kMagic128);              // col c,   K 2qd, 2qd+1
             f[2] = lop3_and_or(shr_mul<4>(x), kNibMask, kMagic128);   // col c,   K 2qd+8, 2qd+9
             f[1] = lop3_and_or(shr_mul<8>(x), kNibMask, kMagic128);   // col c+8, K 2qd, 2qd+1
             f[3] = lop3_and_or(shr_mul<12>(x), kNibMask, kMagic128);  // col c+8, K 2qd+8, 2qd+9
+#endif
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(g[j][nb], f, b[nb][0], b[nb][1]);
         }
@@ -151,7 +158,7 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
     const int m0 = blockIdx.z * kRows;
     const int m_valid = min(kRows, p.m - m0);
     const int chunk0 = blockIdx.y * p.warps_n;
-    const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
+    const uint32_t rank = cluster_ctarank(), csize = (p.debug & 4) ? 1u : cluster_nctarank();
     const int gc0 = min(p.groups, static_cast<int>(rank) * p.groups_per_cta);
     const int gc1 = min(p.groups, gc0 + p.groups_per_cta);
     const int nst = gc1 - gc0;  // stages this CTA streams
@@ -177,7 +184,9 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[j][nb][i] = 0.f;
 
-    if (warp == 0) {
+    if (p.debug & 2) {
+        // timing experiment: no copies, no waits
+    } else if (warp == 0) {
         // ---------------- producer ----------------
         const uint32_t w_row_bytes = static_cast<uint32_t>(p.warps_n) * 512u;
         const uint32_t s_bytes = p.per_column ? 0u : static_cast<uint32_t>(p.warps_n) * 128u;
@@ -228,8 +237,10 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
         const int qd = lane & 3, c = lane >> 2;
         // lane-constant part of the ldmatrix address.  x2: lanes 0-7 rows 0-7 at K+0, lanes 8-15 the same
         // rows at K+8.  x4 adds rows 8-15 for lanes 16-31.
-        const uint32_t a_lane = sA + static_cast<uint32_t>((lane & 7) + (NB == 2 ? (lane >> 4) * 8 : 0)) * p.a_pitch +
-                                static_cast<uint32_t>((lane >> 3) & 1) * 16u;
+        // Only the valid rows are staged: rows past m read the last valid row again (their products land in
+        // accumulator rows that are never stored).
+        const int a_row = min((lane & 7) + (NB == 2 ? (lane >> 4) * 8 : 0), m_valid - 1);
+        const uint32_t a_lane = sA + static_cast<uint32_t>(a_row) * p.a_pitch + static_cast<uint32_t>((lane >> 3) & 1) * 16u;
         const uint32_t w_kt_stride = static_cast<uint32_t>(p.warps_n) * 512u;
         bool ok = true;
         if (wk < nst) ok = mbar_wait(a_full, 0, abort_flag, p.status, 0x1200u);
@@ -259,42 +270,46 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
     __syncthreads();
 
     // ---- reduction over the K-teams of the CTA, then over the CTAs of the cluster -----------
+    // Output pairs (two adjacent columns) are dealt to the cluster ranks in contiguous slices.  Every CTA
+    // sums its K-teams and pushes each pair into the owning rank's receive buffer, slot [sender rank];
+    // after ONE cluster barrier the owner adds the slots in rank order and writes C.  Nobody touches a
+    // peer's shared memory after that barrier, so CTAs may exit without a second one.
     const int pairs_per_row = p.warps_n * 32;
     const int npairs = m_valid * pairs_per_row;
-    if (p.warps_k > 1) {
-        for (int idx = tid; idx < npairs; idx += blockDim.x) {
-            const int row = idx / pairs_per_row, cp = idx - row * pairs_per_row;
-            float *dst = sRed + row * p.red_pitch + 2 * cp;
-            float2 s = *reinterpret_cast<float2 *>(dst);
-            for (int w = 1; w < p.warps_k; ++w) {
-                const float2 v = *reinterpret_cast<float2 *>(dst + static_cast<size_t>(w) * kRows * p.red_pitch);
-                s.x += v.x;
-                s.y += v.y;
-            }
-            *reinterpret_cast<float2 *>(dst) = s;
+    const int per_rank = (npairs + csize - 1) / csize;
+    const uint32_t recv_base = base + p.off_recv;
+    float2 *recv = reinterpret_cast<float2 *>(base_gen + p.off_recv);
+    for (int idx = tid; idx < npairs; idx += blockDim.x) {
+        const int row = idx / pairs_per_row, cp = idx - row * pairs_per_row;
+        const float *src = sRed + row * p.red_pitch + 2 * cp;
+        float2 s = *reinterpret_cast<const float2 *>(src);
+        for (int w = 1; w < p.warps_k; ++w) {
+            const float2 v = *reinterpret_cast<const float2 *>(src + static_cast<size_t>(w) * kRows * p.red_pitch);
+            s.x += v.x;
+            s.y += v.y;
         }
-        __syncthreads();
+        if (csize > 1) {
+            const int owner = idx / per_rank, j = idx - owner * per_rank;
+            st_dsmem_f2(map_to_cta(recv_base + 8u * static_cast<uint32_t>(rank * per_rank + j), owner), s);
+        } else {
+            recv[idx] = s;
+        }
     }
-    if (csize > 1) cluster_sync_all();
+    if (csize > 1)
+        cluster_sync_all();
+    else
+        __syncthreads();
 
     pdl_wait();  // every thread that writes C orders itself after the previous kernel
     const int n0 = chunk0 * 64;
-    const int per_rank = (npairs + csize - 1) / csize;
     const int i0 = min(npairs, static_cast<int>(rank) * per_rank), i1 = min(npairs, i0 + per_rank);
-    const uint32_t red_base = base + p.off_red;
     for (int idx = i0 + tid; idx < i1; idx += blockDim.x) {
         const int row = idx / pairs_per_row, cp = idx - row * pairs_per_row;
-        float2 s;
-        if (csize > 1) {
-            const uint32_t off = red_base + 4u * static_cast<uint32_t>(row * p.red_pitch + 2 * cp);
-            s = make_float2(0.f, 0.f);
-            for (uint32_t r = 0; r < csize; ++r) {
-                const float2 v = ld_dsmem_f2(map_to_cta(off, r));
-                s.x += v.x;
-                s.y += v.y;
-            }
-        } else {
-            s = *reinterpret_cast<const float2 *>(sRed + row * p.red_pitch + 2 * cp);
+        float2 s = recv[idx - i0];
+        for (uint32_t r = 1; r < csize; ++r) {
+            const float2 v = recv[r * per_rank + (idx - i0)];
+            s.x += v.x;
+            s.y += v.y;
         }
         const int col = n0 + 2 * cp;
         if (p.per_column) {
@@ -305,8 +320,6 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
         *reinterpret_cast<__nv_bfloat162 *>(p.C + static_cast<size_t>(m0 + row) * p.n + col) =
             __floats2bfloat162_rn(s.x, s.y);
     }
-    // keep this CTA's shared memory alive until every peer has read it
-    if (csize > 1) cluster_sync_all();
 }
 
 // ---- host: decomposition heuristic and launch ---------------------------------------------
@@ -320,8 +333,8 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // Shared memory one CTA may use so that two CTAs (16 consumer warps) stay resident per SM.
 constexpr int kSmemBudget = 108 * 1024;
 
-int a_stage_bytes(int nb, int groups_per_cta) { return 8 * nb * (groups_per_cta * 256 + 16); }
-int red_bytes(int nb, int wk, int wn) { return 4 * wk * 8 * nb * (wn * 64 + 8); }
+int a_stage_bytes(int rows, int groups_per_cta) { return rows * (groups_per_cta * 256 + 16); }
+int red_bytes(int nb, int wk, int wn) { return 4 * wk * 8 * nb * (wn * 64 + 8) + 8 * (8 * nb * wn * 32 + 8) + 128; }
 
 DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
     DecodeConfig c{};
@@ -357,7 +370,8 @@ DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
     // holds, slots are reused, and then every slot must belong to exactly one K-team (depth a multiple
     // of warps_k): a team that skipped a fill of a slot could not tell fills apart by barrier parity.
     const int stage_bytes = wn * (8 * 512 + 128);
-    const int room = kSmemBudget - a_stage_bytes(c.nb, c.groups_per_cta) - red_bytes(c.nb, wk, wn) - 512;
+    const int rows = m < 8 * c.nb ? m : 8 * c.nb;  // activation rows a CTA stages
+    const int room = kSmemBudget - a_stage_bytes(rows, c.groups_per_cta) - red_bytes(c.nb, wk, wn) - 512;
     int max_stages = room / stage_bytes;
     if (max_stages > 16) max_stages = 16;
     if (max_stages < 1) max_stages = 1;
@@ -388,9 +402,10 @@ int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t strea
     p.a_pitch = c.groups_per_cta * 256 + 16;
     p.stage_bytes = c.warps_n * (8 * 512 + 128);
     p.red_pitch = c.warps_n * 64 + 8;
-    p.off_ring = align(8 * NB * p.a_pitch, 128);
+    p.off_ring = align((m < 8 * NB ? m : 8 * NB) * p.a_pitch, 128);
     p.off_red = p.off_ring + align(c.stages * p.stage_bytes, 128);
-    p.off_bar = p.off_red + align(static_cast<int>(sizeof(float)) * c.warps_k * 8 * NB * p.red_pitch, 128);
+    p.off_recv = p.off_red + align(static_cast<int>(sizeof(float)) * c.warps_k * 8 * NB * p.red_pitch, 128);
+    p.off_bar = p.off_recv + align(8 * (8 * NB * c.warps_n * 32 + c.cluster_k), 128);
     const size_t smem = static_cast<size_t>(p.off_bar) + 8 * (2 * c.stages + 2) + 128;
     if (smem > kMaxSmem) return KILN_W4A16_ERR_KERN_SHAPE;
     cudaLaunchConfig_t cfg = {};
@@ -426,7 +441,8 @@ int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
     if (c.stages < 1 || (c.groups_per_cta > c.stages && c.stages % c.warps_k != 0)) return KILN_W4A16_ERR_KERN_SHAPE;
     // a CTA's K range must fit the activation stage: fall back to more cluster ranks is not possible
     // past 8, so very long K runs go through the register variant, which stages K in passes
-    if (8 * c.nb * (c.groups_per_cta * 256 + 16) > 96 * 1024) return launch_decode_regs(a, DecodeOverride{0, 0, 0});
+    if ((a.m < 8 * c.nb ? a.m : 8 * c.nb) * (c.groups_per_cta * 256 + 16) > 96 * 1024)
+        return launch_decode_regs(a, DecodeOverride{0, 0, 0});
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16 *>(a.A);
     p.B = static_cast<const uint8_t *>(a.B);

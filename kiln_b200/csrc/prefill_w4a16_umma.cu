@@ -44,6 +44,8 @@ struct PrefillParams {
     int m, n, k;
     int m_tiles, n_tiles, splits, k_iters;  // k_iters = k / 64
     int per_column;
+    int stream_k;     // 1: every CTA takes an equal, contiguous share of the (tile, K-step) space
+    int tile_elems;   // rows * columns of one output tile (stream-K slabs are tile-shaped)
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -94,6 +96,49 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
     return d;
 }
+
+// Hands a CTA its work.  Default: units (tile, K-split) dealt round-robin.  Stream-K: the flattened
+// (tile, K-step) space is cut into gridDim.x equal contiguous ranges, so no SM idles in a last partial
+// wave; a range covers the tail of one tile, whole tiles, and the head of another.  Whole tiles are
+// written straight to C; the at most two partial pieces of a CTA go to fp32 slabs 2*cta and 2*cta+1 of
+// the workspace and are summed per tile, in CTA order, by `streamk_fixup_kernel`.  No CTA waits for another.
+struct WorkIter {
+    int mode, u, units, stride, splits, m_tiles, k_iters;
+    long long cur, begin, end;
+    __device__ WorkIter(const PrefillParams &p)
+        : mode(p.stream_k), u(blockIdx.x), units(p.m_tiles * p.n_tiles * p.splits), stride(gridDim.x), splits(p.splits),
+          m_tiles(p.m_tiles), k_iters(p.k_iters) {
+        const long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * p.k_iters;
+        begin = cur = total * blockIdx.x / gridDim.x;
+        end = total * (blockIdx.x + 1) / gridDim.x;
+    }
+    // slab: -1 = the piece is a whole tile (or an ordinary split) and goes where `sp` says; >= 0 = stream-K slab index
+    __device__ bool next(int &mt, int &nt, int &sp, int &ki0, int &ki1, int &slab) {
+        if (mode == 0) {
+            if (u >= units) return false;
+            sp = u % splits;
+            const int t = u / splits;
+            mt = t % m_tiles;
+            nt = t / m_tiles;
+            ki0 = static_cast<int>(static_cast<long long>(k_iters) * sp / splits);
+            ki1 = static_cast<int>(static_cast<long long>(k_iters) * (sp + 1) / splits);
+            slab = -1;
+            u += stride;
+            return true;
+        }
+        if (cur >= end) return false;
+        const int t = static_cast<int>(cur / k_iters);
+        ki0 = static_cast<int>(cur - static_cast<long long>(t) * k_iters);
+        const long long left = end - cur;
+        ki1 = left < k_iters - ki0 ? ki0 + static_cast<int>(left) : k_iters;
+        mt = t % m_tiles;
+        nt = t / m_tiles;
+        sp = 0;
+        slab = (ki0 == 0 && ki1 == k_iters) ? -1 : 2 * static_cast<int>(blockIdx.x) + (cur == begin ? 0 : 1);
+        cur += ki1 - ki0;
+        return true;
+    }
+};
 
 // MT = M-tiles of 128 rows that share one dequantised B stage.  With MT = 2 every weight is dequantised
 // once per 256 rows instead of once per 128, which halves the dequant work per MMA flop; the two
@@ -162,27 +207,16 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_slot;
 
-    const int units = p.m_tiles * p.n_tiles * p.splits;
     const int chunks_n = p.n >> 6;
-
-    // unit -> (m_tile, n_tile, split, k-iteration range)
-    auto decode_unit = [&](int u, int &mt, int &nt, int &sp, int &ki0, int &ki1) {
-        sp = u % p.splits;
-        const int t = u / p.splits;
-        mt = t % p.m_tiles;
-        nt = t / p.m_tiles;
-        ki0 = static_cast<int>(static_cast<long long>(p.k_iters) * sp / p.splits);
-        ki1 = static_cast<int>(static_cast<long long>(p.k_iters) * (sp + 1) / p.splits);
-    };
+    int mt, nt, sp, ki0, ki1, slab;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                int mt, nt, sp, ki0, ki1;
-                decode_unit(u, mt, nt, sp, ki0, ki1);
+            WorkIter wi(p);
+            while (ok && wi.next(mt, nt, sp, ki0, ki1, slab)) {
                 for (int ki = ki0; ki < ki1; ++ki, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
@@ -206,9 +240,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
         if (lane == 0) {
             uint32_t it = 0, tile = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
-                int mt, nt, sp, ki0, ki1;
-                decode_unit(u, mt, nt, sp, ki0, ki1);
+            WorkIter wi(p);
+            for (; ok && wi.next(mt, nt, sp, ki0, ki1, slab); ++tile) {
                 // MT == 1: the two TMEM buffers alternate between tiles.  MT == 2: buffer h holds M-tile h of the pair.
                 const uint32_t acc0 = MT == 1 ? (tile & 1) : 0u, acc_ph = MT == 1 ? ((tile >> 1) & 1) : (tile & 1);
                 for (int ki = ki0; ki < ki1; ++ki, ++it) {
@@ -242,9 +275,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
         uint32_t tile = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
-            int mt, nt, sp, ki0, ki1;
-            decode_unit(u, mt, nt, sp, ki0, ki1);
+        WorkIter wi(p);
+        for (; ok && wi.next(mt, nt, sp, ki0, ki1, slab); ++tile) {
             const uint32_t acc0 = MT == 1 ? (tile & 1) : 0u, acc_ph = MT == 1 ? ((tile >> 1) & 1) : (tile & 1);
 #pragma unroll 1
             for (int h = 0; h < MT && ok; ++h) {
@@ -258,7 +290,15 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(t_row + cc * 32, r);
                 tmem_ld_wait();
-                if (row < p.m) {
+                if (slab >= 0) {
+                    // stream-K piece: tile-shaped fp32 slab, all rows (rows past m hold zeros)
+                    float4 *dst = reinterpret_cast<float4 *>(p.partial + static_cast<size_t>(slab) * p.tile_elems +
+                                                             static_cast<size_t>(h * BM + quarter * 32 + lane) * BN + cc * 32);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v)
+                        dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                             __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                } else if (row < p.m) {
                     const int col = nt * BN + cc * 32;
                     if (p.splits == 1) {
                         uint4 *dst = reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(row) * p.n + col);
@@ -304,9 +344,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
         bool ok = true;
         int cur_group = -1;
         uint32_t s2[8];  // bf16x2 {s, s} for columns 8t + c of this warp's chunk
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-            int mt, nt, sp, ki0, ki1;
-            decode_unit(u, mt, nt, sp, ki0, ki1);
+        WorkIter wi(p);
+        while (ok && wi.next(mt, nt, sp, ki0, ki1, slab)) {
             cur_group = -1;
             auto load_regs = [&](DequantRegs &d, int ki) {
 #pragma unroll
@@ -394,6 +433,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(r_hi + sw_hi), "r"(v[3]) : "memory");
                     }
                 }
+                // every thread publishes its own stores to the async proxy and arrives itself (one arrival per
+                // warp behind a __syncwarp was measured slower: 1154 vs 1217 TFLOP/s on gate+up M=8192)
                 fence_proxy_async_smem();
                 mbar_arrive(full_b(s));
                 r0 = r1;
@@ -442,10 +483,63 @@ __global__ void splitk_reduce_kernel(const float *partial, __nv_bfloat16 *C, con
     }
 }
 
+// Stream-K fix-up: gridDim.y blocks per output tile.  Recomputes which CTAs covered only a part of the tile's
+// K-steps (the same arithmetic as WorkIter), sums their slabs in CTA order and writes bf16.  A tile that
+// one CTA covered completely was already written by that CTA.
+__global__ void streamk_fixup_kernel(const float *partial, __nv_bfloat16 *C, const __half *S, int m, int n, int m_tiles,
+                                     int k_iters, int tile_rows, int bn, int ctas, long long total, int per_column) {
+    const int t = blockIdx.x;
+    const long long t0 = static_cast<long long>(t) * k_iters, t1 = t0 + k_iters;
+    int r_lo = static_cast<int>(t0 * ctas / total) - 1, r_hi = static_cast<int>(t1 * ctas / total) + 1;
+    if (r_lo < 0) r_lo = 0;
+    if (r_hi > ctas - 1) r_hi = ctas - 1;
+    int slabs[40];
+    int ns = 0;
+    for (int r = r_lo; r <= r_hi; ++r) {
+        const long long g0 = total * r / ctas, g1 = total * (r + 1) / ctas;
+        const long long a = g0 > t0 ? g0 : t0, b = g1 < t1 ? g1 : t1;
+        if (a >= b) continue;
+        if (a == t0 && b == t1) return;  // whole tile by one CTA: nothing to fix up
+        if (ns < 40) slabs[ns++] = 2 * r + (a == g0 ? 0 : 1);
+    }
+    const int mt = t % m_tiles, nt = t / m_tiles;
+    const size_t tile_elems = static_cast<size_t>(tile_rows) * bn;
+    const int vec_per_row = bn / 4;
+    // gridDim.y blocks share a tile by rows
+    const int rows_per_block = (tile_rows + gridDim.y - 1) / gridDim.y;
+    const int r_begin = blockIdx.y * rows_per_block;
+    for (int i = threadIdx.x; i < rows_per_block * vec_per_row; i += blockDim.x) {
+        const int rl = r_begin + i / vec_per_row, cv = i % vec_per_row;
+        if (rl >= tile_rows) break;
+        const int row = mt * tile_rows + rl;
+        if (row >= m) continue;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < ns; ++j) {
+            const float4 v = *reinterpret_cast<const float4 *>(partial + slabs[j] * tile_elems +
+                                                               static_cast<size_t>(rl) * bn + 4 * cv);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        const int col = nt * bn + 4 * cv;
+        if (per_column) {
+            const int p0 = scale_single_pos(col), p1 = scale_single_pos(col + 2);
+            acc.x *= __half2float(S[p0]);
+            acc.y *= __half2float(S[p0 + 1]);
+            acc.z *= __half2float(S[p1]);
+            acc.w *= __half2float(S[p1 + 1]);
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(C + static_cast<size_t>(row) * n + col) =
+            make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+    }
+}
+
 // ---- host -----------------------------------------------------------------------------------
 
 struct PrefillConfig {
-    int bn, splits, mt;
+    int bn, splits, mt, stream_k;
 };
 
 // Microseconds per 64-K step of one CTA, from measurements on B200: the dequant warps need about
@@ -459,7 +553,7 @@ double step_us(int bn, int mt) {
 PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
     const int sms = device_sm_count();
     const int k_iters = k / BK;
-    PrefillConfig best{256, 1, 1};
+    PrefillConfig best{256, 1, 1, 0};
     double best_t = 1e30;
     const int bns[2] = {256, 128};
     const int ss[6] = {1, 2, 3, 4, 6, 8};
@@ -478,7 +572,20 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
                 if (s > 1) t += 3.0 + (static_cast<double>(s) + 0.5) * m * static_cast<double>(n) * 4.0 * 2.0 / 4.0e6;
                 if (t < best_t) {
                     best_t = t;
-                    best = PrefillConfig{bn, s, mt};
+                    best = PrefillConfig{bn, s, mt, 0};
+                }
+                // stream-K over the same tiling: equal shares of the K-steps, plus the fix-up pass over the
+                // tiles that end up shared between CTAs (at most one per CTA)
+                if (s == 1 && allow_pairs) {
+                    const long long tiles = static_cast<long long>(m_tiles) * (n / bn);
+                    const double share = static_cast<double>(tiles) * k_iters / sms;
+                    const double tile_mb = BM * mt * bn * 4.0 / 1.0e6;
+                    const double shared_tiles = tiles < sms ? static_cast<double>(tiles) : static_cast<double>(sms);
+                    const double tk = share * step_us(bn, mt) + epi + 1.5 + 6.0 + shared_tiles * tile_mb * 3.0 / 1.5;
+                    if (share >= 8 && tiles * k_iters >= 16LL * sms && k_iters / share + 3 <= 40 && tk < best_t) {
+                        best_t = tk;
+                        best = PrefillConfig{bn, 1, mt, 1};
+                    }
                 }
             }
     return best;
@@ -514,7 +621,7 @@ int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stre
         attr_set[dev] = true;
     }
     const int units = p.m_tiles * p.n_tiles * p.splits;
-    const int grid = units < device_sm_count() ? units : device_sm_count();
+    const int grid = p.stream_k ? device_sm_count() : (units < device_sm_count() ? units : device_sm_count());
     note_launch();
     w4a16_prefill_kernel<BN, MT><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, p);
     return record_cuda_error(cudaGetLastError());
@@ -527,10 +634,12 @@ bool prefill_supported(int m, int n, int k, int groupsize) {
     return m >= 1 && n % 256 == 0 && k % 128 == 0 && k / BK >= 2;
 }
 
-size_t prefill_workspace_bytes(int m, int n, int k) {
-    const PrefillConfig c = choose_prefill(m, n, k);
+size_t workspace_for(const PrefillConfig &c, int m, int n) {
+    if (c.stream_k) return static_cast<size_t>(2) * device_sm_count() * (BM * c.mt) * c.bn * sizeof(float);
     return c.splits > 1 ? static_cast<size_t>(c.splits) * m * n * sizeof(float) : 0;
 }
+
+size_t prefill_workspace_bytes(int m, int n, int k) { return workspace_for(choose_prefill(m, n, k), m, n); }
 
 int launch_prefill(const GemmArgs &a) {
     EncodeTiledFn enc = encode_fn();
@@ -563,8 +672,10 @@ int launch_prefill(const GemmArgs &a) {
     p.splits = c.splits;
     p.k_iters = a.k / BK;
     p.per_column = a.groupsize == -1;
-    if (c.splits > 1 && (!a.workspace || a.workspace_bytes < static_cast<size_t>(c.splits) * a.m * a.n * sizeof(float)))
-        return KILN_W4A16_ERR_WORKSPACE;
+    p.stream_k = c.stream_k;
+    p.tile_elems = BM * c.mt * c.bn;
+    const size_t need = workspace_for(c, a.m, a.n);
+    if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
 
     int rc;
     if (c.mt == 2)
@@ -579,6 +690,14 @@ int launch_prefill(const GemmArgs &a) {
         if (blocks > cap) blocks = cap;
         note_launch();
         splitk_reduce_kernel<<<blocks, 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, c.splits, p.per_column);
+        rc = record_cuda_error(cudaGetLastError());
+    }
+    if (c.stream_k) {
+        const long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * p.k_iters;
+        note_launch();
+        streamk_fixup_kernel<<<dim3(p.m_tiles * p.n_tiles, 16), 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, p.m_tiles, p.k_iters,
+                                                                         BM * c.mt, c.bn, device_sm_count(), total,
+                                                                         p.per_column);
         rc = record_cuda_error(cudaGetLastError());
     }
     return rc;

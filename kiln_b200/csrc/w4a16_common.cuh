@@ -92,6 +92,10 @@ __device__ __forceinline__ float2 ld_dsmem_f2(uint32_t cluster_addr) {
     return v;
 }
 
+__device__ __forceinline__ void st_dsmem_f2(uint32_t cluster_addr, float2 v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1,%2};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
 // Position of natural column `col` inside the per-column (groupsize -1) scale order
 // (kiln-marlin-gemm/src/lib.rs:348-357): within each 32, out[8i + j] = in[2i + {0,1,8,9,16,17,24,25}[j]].
 __device__ __host__ __forceinline__ int scale_single_pos(int col) {

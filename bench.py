@@ -285,6 +285,63 @@ def prefill_detail(d: Device, peaks):
     return out
 
 
+def stack_detail(d: Device, m: int = 64):
+    """Config 3: a 32-layer Qwen3.5-4B-like projection stack (24 GDN layers: GDN-in, GDN-out, gate+up, down; 8
+    attention layers: q, k, v, o, gate+up, down = 144 GEMMs, distinct random int4 weights per layer, 1.6 GB, so
+    every GEMM streams from HBM) at continuous-batch M, activations carried layer to layer.  Between GEMMs
+    there are cheap torch elementwise adapters standing in for attention / GDN mixing (slice, SwiGLU,
+    residual add, RMS normalisation); they are part of `stack_us`, and `gemm_only_us` is the same 144 GEMMs
+    captured without them."""
+    t = d.torch
+    layers = []
+    for li in range(32):
+        attn = li % 4 == 3
+        names = ["q", "k", "v", "o", "gate_up", "down"] if attn else ["gdn_in", "gdn_out", "gate_up", "down"]
+        layers.append((attn, {nm: d.weights(*SHAPES[nm], 1)[0] for nm in names}))
+    h0 = d.acts(m, 2560)
+
+    def norm(x):
+        xf = x.float()
+        return (xf * t.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)).to(t.bfloat16)
+
+    def gemm(x, w):
+        o = t.empty((x.shape[0], w[1].shape[1]), dtype=t.bfloat16, device=d.dev)
+        return d.gemm(x, w, o)
+
+    def forward(with_adapters=True):
+        h = h0
+        for attn, w in layers:
+            x = norm(h) if with_adapters else h
+            if attn:
+                q = gemm(x, w["q"])
+                k_ = gemm(x, w["k"])
+                v_ = gemm(x, w["v"])
+                mix = q + t.cat([k_, v_] * 4, dim=1) if with_adapters else q  # stand-in for attention
+                o = gemm(mix, w["o"])
+            else:
+                z = gemm(x, w["gdn_in"])
+                mix = (z[:, :4096] * t.sigmoid(z[:, 4096:].float()).to(t.bfloat16)) if with_adapters else z[:, :4096].contiguous()
+                o = gemm(mix, w["gdn_out"])
+            h = (h + o) if with_adapters else o
+            x = norm(h) if with_adapters else h
+            gu = gemm(x, w["gate_up"])
+            act = (t.nn.functional.silu(gu[:, :9216].float()).to(t.bfloat16) * gu[:, 9216:]) if with_adapters else gu[:, :9216].contiguous()
+            dn = gemm(act, w["down"])
+            h = (h + dn) if with_adapters else dn
+        return h
+
+    out = {"m": m, "gemms": 144, "weight_GB": round(sum(alg_bytes(0, *SHAPES[nm]) for a_, w in layers for nm in w) / 1e9, 3)}
+    for key, flag in (("stack_us", True), ("gemm_only_us", False)):
+        out[key] = round(d.time_graph(lambda: forward(flag), 1, reps=7), 1)
+    bytes_total = sum(alg_bytes(m, *SHAPES[nm]) for a_, w in layers for nm in w)
+    flops_total = sum(alg_flops(m, *SHAPES[nm]) for a_, w in layers for nm in w)
+    out["gemm_only_GBps"] = round(bytes_total / out["gemm_only_us"] / 1e3, 1)
+    out["gemm_only_TFLOPs"] = round(flops_total / out["gemm_only_us"] / 1e6, 1)
+    out["ideal_us_at_measured_hbm"] = round(bytes_total / load_peaks()["hbm_gbs"] / 1e3, 1)
+    del layers
+    return out
+
+
 def sharded_detail(d: Device, world: int, rank: int):
     """The path's N-sharded configuration: M=16384, K=9216, N=73728 split by columns over the ranks, local
     GEMM + NCCL all-gather of the bf16 slices (blocked [g, M, N/g] result).  Times are max over ranks."""
@@ -484,6 +541,7 @@ def run_ours(args):
         del h_in, h_out, d_in
         line["decode"] = decode_detail(d, peaks)
         line["prefill"] = prefill_detail(d, peaks)
+        line["stack_m64"] = stack_detail(d, 64)
         if world == 1:
             cases = cpu_sweep_inputs()
             cpu_sweep_once(cases)

@@ -140,8 +140,9 @@ kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detai
  * Process-wide, not thread-safe; has no counterpart in the reference. */
 void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
 
-/* Tuning hook: the M at and above which the tcgen05 prefill kernel is used
- * (default 128).  <= 0 restores the default; a huge value disables that kernel. */
+/* Tuning hook: the M at and above which the tcgen05 prefill kernel is used.  <= 0 restores the
+ * built-in rule (M >= 64, or M >= 17 for weights of 16 M elements and more); a huge value
+ * disables that kernel. */
 void kiln_w4a16_set_prefill_min_m(int min_m);
 
 /* Library version, and number of kernels this library launched since load

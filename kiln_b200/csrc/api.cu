@@ -15,8 +15,8 @@ namespace {
 std::atomic<unsigned long long> g_launches{0};
 thread_local int t_last_cuda_error = 0;
 DecodeOverride g_decode_override{0, 0, 0};
-std::atomic<int> g_prefill_min_m{128};
-constexpr int kDefaultPrefillMinM = 128;
+constexpr int kDefaultPrefillMinM = 0;  // 0 = the built-in rule
+std::atomic<int> g_prefill_min_m{kDefaultPrefillMinM};
 }  // namespace
 
 void note_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -72,8 +72,17 @@ static int validate(const GemmArgs &a) {
     return -1;  // proceed
 }
 
+// Kernel choice by M (measured on B200): the decode kernel handles 8 or 16 rows per pass and repeats the
+// int4 dequant for every pass, the tcgen05 kernel dequantises once per 128 rows.  With the default threshold
+// the tcgen05 kernel takes over at M >= 17 for large weights (>= 16 M elements: gate+up, down, GDN-in) and at
+// M >= 64 for the small ones, where its 128 x 128 tiles leave most SMs idle.  kiln_w4a16_set_prefill_min_m
+// replaces the rule by a plain threshold.
 static bool use_prefill(int m, int n, int k, int groupsize) {
-    return m >= g_prefill_min_m.load(std::memory_order_relaxed) && prefill_supported(m, n, k, groupsize);
+    if (!prefill_supported(m, n, k, groupsize)) return false;
+    const int min_m = g_prefill_min_m.load(std::memory_order_relaxed);
+    if (min_m != kDefaultPrefillMinM) return m >= min_m;
+    if (m >= 64) return true;
+    return m >= 17 && static_cast<long long>(n) * k >= (16LL << 20);
 }
 
 static int gemm(const GemmArgs &a) {

@@ -19,8 +19,6 @@
 //    the CTAs of a thread-block cluster; partial tiles meet in (distributed) shared memory
 //    and are summed in a fixed order, so results are bit-reproducible.
 //  * every wait on an mbarrier is bounded (see w4a16_async.cuh).
-#include <cstdlib>
-
 #include "w4a16_async.cuh"
 
 namespace kiln {
@@ -42,7 +40,6 @@ struct DecodeParams {
     int red_pitch;       // floats per reduction row (warps_n*64 + 8)
     // shared-memory carve-up (bytes from the 128-byte aligned base)
     int off_ring, off_red, off_recv, off_bar, stage_bytes;
-    int debug;  // bit0: skip compute, bit1: skip reduce
 };
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t w, int hi) {
@@ -107,17 +104,10 @@ __device__ __forceinline__ void compute_stage(uint32_t w_addr, uint32_t w_kt_str
         for (int j = 0; j < 4; ++j) {
             const uint32_t x = xs[j];
             uint32_t f[4];
-#if defined(KILN_DECODE_NODEQ)
-            f[0] = x; f[1] = x; f[2] = x; f[3] = x;
-#elif defined(KILN_DECODE_NOSHIFT)
-            f[0] = lop3_and_or(x, kNibMask, kMagic128); f[1] = lop3_and_or(x, 0x00F000F0u, kMagic128);
-            f[2] = lop3_and_or(x, 0x0F000F00u, kMagic128); f[3] = lop3_and_or(x, 0xF000F000u, kMagic128);
-#else
             f[0] = lop3_and_or(x, kNibMask, kMagic128);              // col c,   K 2qd, 2qd+1
             f[2] = lop3_and_or(shr_mul<4>(x), kNibMask, kMagic128);   // col c,   K 2qd+8, 2qd+9
             f[1] = lop3_and_or(shr_mul<8>(x), kNibMask, kMagic128);   // col c+8, K 2qd, 2qd+1
             f[3] = lop3_and_or(shr_mul<12>(x), kNibMask, kMagic128);  // col c+8, K 2qd+8, 2qd+9
-#endif
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(g[j][nb], f, b[nb][0], b[nb][1]);
         }
@@ -158,7 +148,7 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
     const int m0 = blockIdx.z * kRows;
     const int m_valid = min(kRows, p.m - m0);
     const int chunk0 = blockIdx.y * p.warps_n;
-    const uint32_t rank = cluster_ctarank(), csize = (p.debug & 4) ? 1u : cluster_nctarank();
+    const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
     const int gc0 = min(p.groups, static_cast<int>(rank) * p.groups_per_cta);
     const int gc1 = min(p.groups, gc0 + p.groups_per_cta);
     const int nst = gc1 - gc0;  // stages this CTA streams
@@ -184,9 +174,7 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[j][nb][i] = 0.f;
 
-    if (p.debug & 2) {
-        // timing experiment: no copies, no waits
-    } else if (warp == 0) {
+    if (warp == 0) {
         // ---------------- producer ----------------
         const uint32_t w_row_bytes = static_cast<uint32_t>(p.warps_n) * 512u;
         const uint32_t s_bytes = p.per_column ? 0u : static_cast<uint32_t>(p.warps_n) * 128u;
@@ -249,7 +237,7 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
             const uint32_t ph = (i / p.stages) & 1;
             if (!(ok = mbar_wait(full(s), ph, abort_flag, p.status, 0x1300u | s))) break;
             const uint32_t st = sRing + s * p.stage_bytes;
-            if (!(p.debug & 1)) compute_stage<NB>(st + wn * 512u + lane * 16u, w_kt_stride, st + 8u * w_kt_stride + wn * 128u + 16u * c,
+            compute_stage<NB>(st + wn * 512u + lane * 16u, w_kt_stride, st + 8u * w_kt_stride + wn * 128u + 16u * c,
                               !p.per_column, a_lane + static_cast<uint32_t>(i) * 256u, acc);
             __syncwarp();
             if (lane == 0) mbar_arrive(empty(s));
@@ -458,7 +446,6 @@ int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
     p.warps_k = c.warps_k;
     p.stages = c.stages;
     p.per_column = a.groupsize == -1;
-    { const char *e = getenv("KILN_W4A16_DEBUG"); p.debug = e ? atoi(e) : 0; }
     if (c.nb == 1) return launch_one<1>(p, c, a.m, a.stream);
     return launch_one<2>(p, c, a.m, a.stream);
 }

@@ -30,9 +30,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kNumThreads = 14 * 32;
 constexpr int kDequantWarp0 = 6;
-constexpr int kNumDequantThreads = 8 * 32;
 constexpr int kNumEpilogueThreads = 4 * 32;
 
 struct PrefillParams {
@@ -143,15 +141,18 @@ struct WorkIter {
 // MT = M-tiles of 128 rows that share one dequantised B stage.  With MT = 2 every weight is dequantised
 // once per 256 rows instead of once per 128, which halves the dequant work per MMA flop; the two
 // accumulators then take both TMEM buffers, so the epilogue only partly overlaps the next tile.
-template <int BN, int MT = 1>
+template <int BN, int MT = 1, int DW = 8>
 struct Cfg {
+    // producer, MMA, 4 epilogue and DW dequant warps (16 dequant warps were measured no faster than 8)
+    static constexpr int kThreads = (6 + DW) * 32;
     static constexpr int kABytes = MT * BM * BK * 2;  // 16 KB per M-tile
     static constexpr int kStages = (192 * 1024) / (kABytes + BN * BK * 2);
     static constexpr int kBBytes = BN * BK * 2;  // 32 / 16 KB
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBlocksPerStage = (BN / 64) * 4;  // 512-byte packed blocks per stage
-    static constexpr int kBlocksPerWarp = kBlocksPerStage / 8;
+    static constexpr int kBlocksPerWarp = kBlocksPerStage / DW;
+    static_assert(kBlocksPerStage % DW == 0, "dequant warps must divide the packed blocks of a stage");
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
     // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
@@ -163,10 +164,10 @@ struct DequantRegs {
     uint4 w[2];
 };
 
-template <int BN, int MT>
-__global__ void __launch_bounds__(kNumThreads, 1)
+template <int BN, int MT, int DW>
+__global__ void __launch_bounds__((6 + DW) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillParams p) {
-    using C = Cfg<BN, MT>;
+    using C = Cfg<BN, MT, DW>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -185,7 +186,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_a(s), 1);
-            mbar_init(full_b(s), kNumDequantThreads);
+            mbar_init(full_b(s), DW * 32);
             mbar_init(empty(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -350,7 +351,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             auto load_regs = [&](DequantRegs &d, int ki) {
 #pragma unroll
                 for (int b = 0; b < C::kBlocksPerWarp; ++b) {
-                    const int blk = dw + 8 * b;
+                    const int blk = dw + DW * b;
                     const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
                     const size_t idx =
                         (static_cast<size_t>(ki * 4 + kt) * chunks_n + nt * kChunksPerTile + ch) * 32 + lane;
@@ -402,7 +403,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 const uint32_t b_tile = smem_base + s * C::kStageBytes + C::kABytes;
 #pragma unroll
                 for (int b = 0; b < C::kBlocksPerWarp; ++b) {
-                    const int blk = dw + 8 * b;
+                    const int blk = dw + DW * b;
                     const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
                     const uint32_t xs[4] = {r0.w[b].x, r0.w[b].y, r0.w[b].z, r0.w[b].w};
                     // row (= column of B) n_local = ch*64 + 8t + c, 128 B per row; 16-byte chunk (2kt + half) ^ c
@@ -581,7 +582,7 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
                     const double share = static_cast<double>(tiles) * k_iters / sms;
                     const double tile_mb = BM * mt * bn * 4.0 / 1.0e6;
                     const double shared_tiles = tiles < sms ? static_cast<double>(tiles) : static_cast<double>(sms);
-                    const double tk = share * step_us(bn, mt) + epi + 1.5 + 6.0 + shared_tiles * tile_mb * 3.0 / 1.5;
+                    const double tk = share * step_us(bn, mt) + epi * (share / k_iters + 1.0) + 1.5 + 6.0 + shared_tiles * tile_mb * 3.0 / 1.5;
                     if (share >= 8 && tiles * k_iters >= 16LL * sms && k_iters / share + 3 <= 40 && tk < best_t) {
                         best_t = tk;
                         best = PrefillConfig{bn, 1, mt, 1};
@@ -608,14 +609,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BN, int MT = 1>
+template <int BN, int MT = 1, int DW = 8>
 int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stream) {
-    using C = Cfg<BN, MT>;
+    using C = Cfg<BN, MT, DW>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT>,
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW>,
                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
             return rc;
         attr_set[dev] = true;
@@ -623,7 +624,7 @@ int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stre
     const int units = p.m_tiles * p.n_tiles * p.splits;
     const int grid = p.stream_k ? device_sm_count() : (units < device_sm_count() ? units : device_sm_count());
     note_launch();
-    w4a16_prefill_kernel<BN, MT><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, p);
+    w4a16_prefill_kernel<BN, MT, DW><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, p);
     return record_cuda_error(cudaGetLastError());
 }
 

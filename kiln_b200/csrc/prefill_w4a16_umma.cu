@@ -141,8 +141,11 @@ struct WorkIter {
 // MT = M-tiles of 128 rows that share one dequantised B stage.  With MT = 2 every weight is dequantised
 // once per 256 rows instead of once per 128, which halves the dequant work per MMA flop; the two
 // accumulators then take both TMEM buffers, so the epilogue only partly overlaps the next tile.
-template <int BN, int MT = 1, int DW = 8>
+// DG = dequant groups: the DW dequant warps are split into DG teams that fill alternate stages, so the
+// dequant of stage s+1 runs beside that of stage s instead of after it.
+template <int BN, int MT = 1, int DW = 8, int DG = 2>
 struct Cfg {
+    static constexpr int kGroupWarps = DW / DG;
     // producer, MMA, 4 epilogue and DW dequant warps (16 dequant warps were measured no faster than 8)
     static constexpr int kThreads = (6 + DW) * 32;
     static constexpr int kABytes = MT * BM * BK * 2;  // 16 KB per M-tile
@@ -151,8 +154,9 @@ struct Cfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kBlocksPerStage = (BN / 64) * 4;  // 512-byte packed blocks per stage
-    static constexpr int kBlocksPerWarp = kBlocksPerStage / DW;
-    static_assert(kBlocksPerStage % DW == 0, "dequant warps must divide the packed blocks of a stage");
+    static constexpr int kBlocksPerWarp = kBlocksPerStage / kGroupWarps;
+    static_assert(kBlocksPerStage % kGroupWarps == 0 && kGroupWarps % (BN / 64) == 0,
+                  "a dequant team must divide the packed blocks of a stage and keep one chunk per warp");
     static constexpr int kBarrierBytes = 1024;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
     // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
@@ -160,14 +164,16 @@ struct Cfg {
                                        (static_cast<uint32_t>(BM >> 4) << 24);
 };
 
+template <int NBLK>
 struct DequantRegs {
-    uint4 w[2];
+    uint4 w[NBLK];
 };
 
-template <int BN, int MT, int DW>
+template <int BN, int MT, int DW, int DG>
 __global__ void __launch_bounds__((6 + DW) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillParams p) {
-    using C = Cfg<BN, MT, DW>;
+    using C = Cfg<BN, MT, DW, DG>;
+    using Regs = DequantRegs<C::kBlocksPerWarp>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -186,7 +192,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_a(s), 1);
-            mbar_init(full_b(s), DW * 32);
+            mbar_init(full_b(s), C::kGroupWarps * 32);  // the threads of the team that fills the stage
             mbar_init(empty(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -338,20 +344,20 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
         }
     } else {
         // ---------------- dequant: packed int4 -> bf16 B tile ----------------
-        const int dw = warp - kDequantWarp0;
+        const int dw = (warp - kDequantWarp0) / DG, team = (warp - kDequantWarp0) % DG;  // warp `dw` of team `team`
         const int qd = lane & 3, c = lane >> 2;
         constexpr int kChunksPerTile = BN / 64;
-        uint32_t it = 0;
+        uint32_t it_base = 0;  // stages issued before this piece of work (all teams count alike)
         bool ok = true;
         int cur_group = -1;
         uint32_t s2[8];  // bf16x2 {s, s} for columns 8t + c of this warp's chunk
         WorkIter wi(p);
         while (ok && wi.next(mt, nt, sp, ki0, ki1, slab)) {
             cur_group = -1;
-            auto load_regs = [&](DequantRegs &d, int ki) {
+            auto load_regs = [&](Regs &d, int ki) {
 #pragma unroll
                 for (int b = 0; b < C::kBlocksPerWarp; ++b) {
-                    const int blk = dw + DW * b;
+                    const int blk = dw + C::kGroupWarps * b;
                     const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
                     const size_t idx =
                         (static_cast<size_t>(ki * 4 + kt) * chunks_n + nt * kChunksPerTile + ch) * 32 + lane;
@@ -364,15 +370,18 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             };
             uint4 sv_next = make_uint4(0, 0, 0, 0);
             int next_group = -1;
-            if (!p.per_column) {
-                next_group = ki0 >> 1;
+            // this team's K-steps of the piece: those whose stage number is congruent to `team`
+            const int kf = ki0 + static_cast<int>((static_cast<uint32_t>(team) + DG - it_base % DG) % DG);
+            if (!p.per_column && kf < ki1) {
+                next_group = kf >> 1;
                 sv_next = load_scales(next_group);
             }
-            DequantRegs r0, r1, r2;  // packed words of K-steps ki, ki+1, ki+2: three L2 round trips in flight
-            load_regs(r0, ki0);
-            if (ki0 + 1 < ki1) load_regs(r1, ki0 + 1);
-            if (ki0 + 2 < ki1) load_regs(r2, ki0 + 2);
-            for (int ki = ki0; ki < ki1; ++ki, ++it) {
+            Regs r0, r1, r2;  // packed words of this team's next three K-steps: three L2 round trips in flight
+            if (kf < ki1) load_regs(r0, kf);
+            if (kf + DG < ki1) load_regs(r1, kf + DG);
+            if (kf + 2 * DG < ki1) load_regs(r2, kf + 2 * DG);
+            for (int ki = kf; ki < ki1; ki += DG) {
+                const uint32_t it = it_base + static_cast<uint32_t>(ki - ki0);
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1;
                 // scales of this K group (all blocks of a warp share one chunk: blk % kChunksPerTile == dw % ..)
@@ -385,9 +394,9 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     } else {
                         // the scales of this group were requested when the previous group started
                         const uint4 sv = (next_group == g) ? sv_next : load_scales(g);
-                        if (g + 1 <= ((ki1 - 1) >> 1)) {
-                            sv_next = load_scales(g + 1);
-                            next_group = g + 1;
+                        if (ki + DG < ki1 && ((ki + DG) >> 1) != g) {  // the group of this team's next K-step
+                            sv_next = load_scales((ki + DG) >> 1);
+                            next_group = (ki + DG) >> 1;
                         }
                         const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
@@ -403,7 +412,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 const uint32_t b_tile = smem_base + s * C::kStageBytes + C::kABytes;
 #pragma unroll
                 for (int b = 0; b < C::kBlocksPerWarp; ++b) {
-                    const int blk = dw + DW * b;
+                    const int blk = dw + C::kGroupWarps * b;
                     const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
                     const uint32_t xs[4] = {r0.w[b].x, r0.w[b].y, r0.w[b].z, r0.w[b].w};
                     // row (= column of B) n_local = ch*64 + 8t + c, 128 B per row; 16-byte chunk (2kt + half) ^ c
@@ -440,8 +449,9 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 mbar_arrive(full_b(s));
                 r0 = r1;
                 r1 = r2;
-                if (ki + 3 < ki1) load_regs(r2, ki + 3);
+                if (ki + 3 * DG < ki1) load_regs(r2, ki + 3 * DG);
             }
+            it_base += static_cast<uint32_t>(ki1 - ki0);
         }
     }
 
@@ -609,14 +619,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int BN, int MT = 1, int DW = 8>
+template <int BN, int MT = 1, int DW = 8, int DG = 2>
 int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stream) {
-    using C = Cfg<BN, MT, DW>;
+    using C = Cfg<BN, MT, DW, DG>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW>,
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG>,
                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
             return rc;
         attr_set[dev] = true;
@@ -624,7 +634,7 @@ int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stre
     const int units = p.m_tiles * p.n_tiles * p.splits;
     const int grid = p.stream_k ? device_sm_count() : (units < device_sm_count() ? units : device_sm_count());
     note_launch();
-    w4a16_prefill_kernel<BN, MT, DW><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, p);
+    w4a16_prefill_kernel<BN, MT, DW, DG><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, p);
     return record_cuda_error(cudaGetLastError());
 }
 

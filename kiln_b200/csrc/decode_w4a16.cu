@@ -35,6 +35,7 @@ struct DecodeParams {
     int groups_per_cta;  // K groups owned by one CTA of the cluster
     int warps_n, warps_k;
     int stages;          // ring depth
+    int window;          // stages kept in flight by the producer
     int per_column;      // groupsize == -1: one scale row, applied at the end
     int a_pitch;         // bytes per staged activation row (groups_per_cta*256 + 16)
     int red_pitch;       // floats per reduction row (warps_n*64 + 8)
@@ -194,8 +195,12 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
             else if (lane == 8 && s_bytes)
                 bulk_g2s(dst + 8 * w_row_bytes, p.S + static_cast<size_t>(g) * p.n + chunk0 * 64, s_bytes, full(s));
         };
-        // weights never depend on the previous kernel: fill the ring first
-        const int pre = min(nst, p.stages);
+        // Weights never depend on the previous kernel: start them before waiting for it.  Only `window`
+        // stages are kept in flight per CTA: requesting everything at once makes the memory system serve all
+        // copies side by side, so that the first stage lands about as late as the last (measured: first
+        // data after 4.2 us instead of ~1.3 us) and the consumers start late.
+        const int window = min(p.window, p.stages);
+        const int pre = min(nst, window);
         for (int i = 0; i < pre; ++i) issue_stage(i);
         pdl_wait();
         // activations: one bulk copy per valid row, K range of this CTA
@@ -208,9 +213,12 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
                          a_row_bytes, a_full);
         }
         for (int i = pre; i < nst && ok; ++i) {
-            const int s = i % p.stages;
-            const uint32_t ph = (i / p.stages) & 1;
-            ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x1100u | s);
+            const int j = i - window;  // this stage must have landed before stage i is requested
+            ok = mbar_wait(full(j % p.stages), (j / p.stages) & 1, abort_flag, p.status, 0x1000u | (j % p.stages));
+            if (ok && i >= p.stages) {  // slot reuse: its previous contents must have been consumed
+                const int s = i % p.stages;
+                ok = mbar_wait(empty(s), ((i / p.stages) & 1) ^ 1, abort_flag, p.status, 0x1100u | s);
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (ok) issue_stage(i);
         }
@@ -240,7 +248,7 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
             compute_stage<NB>(st + wn * 512u + lane * 16u, w_kt_stride, st + 8u * w_kt_stride + wn * 128u + 16u * c,
                               !p.per_column, a_lane + static_cast<uint32_t>(i) * 256u, acc);
             __syncwarp();
-            if (lane == 0) mbar_arrive(empty(s));
+            if (lane == 0 && nst > p.stages) mbar_arrive(empty(s));  // only a reused slot needs the release
         }
         // this warp's partial tile -> shared memory: acc[j][nb][i] is column 16j + c + 8*(i/2) of the chunk,
         // batch row 8nb + 2qd + (i%2)
@@ -287,7 +295,6 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
         cluster_sync_all();
     else
         __syncthreads();
-
     pdl_wait();  // every thread that writes C orders itself after the previous kernel
     const int n0 = chunk0 * 64;
     const int i0 = min(npairs, static_cast<int>(rank) * per_rank), i1 = min(npairs, i0 + per_rank);
@@ -445,6 +452,7 @@ int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
     p.warps_n = c.warps_n;
     p.warps_k = c.warps_k;
     p.stages = c.stages;
+    p.window = 4;
     p.per_column = a.groupsize == -1;
     if (c.nb == 1) return launch_one<1>(p, c, a.m, a.stream);
     return launch_one<2>(p, c, a.m, a.stream);

@@ -367,6 +367,30 @@ def sharded_detail(d: Device, world: int, rank: int):
         t.cuda.synchronize()
         return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[0].elapsed_time(e[2])
 
+    fused_ms = None
+    if world > 1:
+        import kiln_b200
+        from kiln_b200 import MarlinPackedProj
+
+        lin = kiln_b200.ColumnParallelLinear(MarlinPackedProj(w[0], w[1], 128, k, nl), rank, world, None)
+        sym = kiln_b200.FusedGatherOutput(m, n, d.dev)
+
+        def fused_once():
+            e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            e0.record()
+            kiln_b200.fused_column_parallel_gemm(a, lin, sym)  # GEMM with peer-store epilogue + barrier
+            e1.record()
+            t.cuda.synchronize()
+            return e0.elapsed_time(e1)
+
+        fused_once()
+        fused_once()
+        dist.barrier()
+        fl = sorted(fused_once() for _ in range(3))[1]
+        tt = t.tensor([fl], device=d.dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        fused_ms = float(tt.item())
+        del sym
     once()
     once()
     if world > 1:
@@ -384,6 +408,9 @@ def sharded_detail(d: Device, world: int, rank: int):
         "TFLOPs_total_end_to_end": round(flops / med[2] / 1e9, 1),
         "allgather_GBps_per_gpu_recv": round((world - 1) * m * nl * 2 / med[1] / 1e6, 1) if world > 1 else None,
         "layout": "blocked [g, M, N/g]", "scaling": "strong",
+        "fused_gemm_allgather_ms": round(fused_ms, 3) if fused_ms else None,
+        "fused_TFLOPs_total": round(flops / fused_ms / 1e9, 1) if fused_ms else None,
+        "fused_layout": "row-major [M, N] on every GPU (peer stores from the GEMM epilogue + one barrier)",
     }
     del w, a, local, gathered
     return out

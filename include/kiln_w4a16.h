@@ -83,6 +83,20 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
 kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const void *B, void *C, const void *s, int m,
                                                  int n, int k, int groupsize, void *stream);
 
+/* Column-parallel GEMM with the all-gather fused into its epilogue.  The reference is single-GPU (its
+ * wrapper hard-codes device 0, crates/kiln-marlin-gemm/src/lib.rs:210-215); this replaces "GEMM on the local
+ * columns + ncclAllGather of the slices".  B [k/16, 2*n_local] and s [k/g, n_local] are this rank's column
+ * slice.  C_peers is a HOST array of n_peers (1..8) device pointers, one per GPU of the group (this GPU's
+ * own buffer included), each a row-major bf16 [m, ldc] buffer mapped into this process (peer access /
+ * symmetric memory).  The tcgen05 kernel stores every finished 16-byte piece of rows x columns
+ * [col0, col0 + n_local) into all of them with plain stores over NVLink; no TMA and no multicast is
+ * involved.  The call returns when the launch is enqueued; the gathered matrix is complete on a GPU once
+ * every rank's launch has finished, so callers follow it with a stream-ordered barrier across the group
+ * (kiln_b200.shard does).  ldc and col0 are in elements and multiples of 8. */
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather(const void *A, const void *B, const void *s, int m, int n_local,
+                                                   int k, int groupsize, void *const *C_peers, int n_peers, int ldc,
+                                                   int col0, void *stream);
+
 /* Scratch bytes the GEMM needs for (m, n, k); replaces the reference wrapper's
  * fixed `(n/128) * 16` int32 lock array (crates/kiln-marlin-gemm/src/lib.rs:176-178). */
 size_t kiln_w4a16_workspace_bytes(int m, int n, int k);

@@ -8,6 +8,8 @@ from . import pack  # noqa: F401
 from .marlin_gemm import KilnMarlinError, marlin_w4a16_gemm, workspace_bytes  # noqa: F401
 from .shard import (  # noqa: F401
     ColumnParallelLinear,
+    FusedGatherOutput,
+    fused_column_parallel_gemm,
     all_gather_columns,
     shard_bounds,
     shard_packed,
@@ -24,5 +26,5 @@ from .marlin_proj import (  # noqa: F401
 __all__ = [
     "pack", "marlin_w4a16_gemm", "workspace_bytes", "KilnMarlinError", "MarlinPackedProj",
     "matmul_bf16", "pack_from_bf16", "pack_from_bf16_batch", "shape_is_supported",
-    "ColumnParallelLinear", "all_gather_columns", "shard_bounds", "shard_packed", "shard_proj",
+    "ColumnParallelLinear", "FusedGatherOutput", "fused_column_parallel_gemm", "all_gather_columns", "shard_bounds", "shard_packed", "shard_proj",
 ]

@@ -131,6 +131,26 @@ kiln_w4a16_status_t kiln_marlin_w4a16_gemm(const void *A, const void *B, void *C
     return gemm(a);
 }
 
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather(const void *A, const void *B, const void *s, int m, int n_local,
+                                                   int k, int groupsize, void *const *C_peers, int n_peers, int ldc,
+                                                   int col0, void *stream) {
+    if (!C_peers || n_peers < 1 || n_peers > 8) return KILN_W4A16_ERR_ARG;
+    if (ldc < col0 + n_local || col0 < 0 || ldc % 8 != 0 || col0 % 8 != 0) return KILN_W4A16_ERR_ARG;
+    GemmArgs a{A, B, s, C_peers[0], m, n_local, k, groupsize, nullptr, 0, static_cast<cudaStream_t>(stream)};
+    const int v = validate(a);
+    if (v >= 0) return v;
+    if (!prefill_supported(m, n_local, k, groupsize)) return KILN_W4A16_ERR_KERN_SHAPE;
+    for (int i = 0; i < n_peers; ++i) {
+        if (!C_peers[i]) return KILN_W4A16_ERR_ARG;
+        if (reinterpret_cast<uintptr_t>(C_peers[i]) & 15) return KILN_W4A16_ERR_ALIGNMENT;
+        a.peer_c[i] = C_peers[i];
+    }
+    a.n_peers = n_peers;
+    a.ldc = ldc;
+    a.col0 = col0;
+    return launch_prefill(a);
+}
+
 size_t kiln_w4a16_workspace_bytes(int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
     if (use_prefill(m, n, k, 128)) return prefill_workspace_bytes(m, n, k);

@@ -31,6 +31,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kDequantWarp0 = 6;
+constexpr uint32_t kEpiPitch = 144;                 // bytes per staged epilogue row (128 + 16 against bank conflicts)
+constexpr uint32_t kEpiWarpBytes = 32 * kEpiPitch;  // per epilogue warp: 32 rows x 64 columns of bf16
 constexpr int kNumEpilogueThreads = 4 * 32;
 
 struct PrefillParams {
@@ -42,6 +44,10 @@ struct PrefillParams {
     int m, n, k;
     int m_tiles, n_tiles, splits, k_iters;  // k_iters = k / 64
     int per_column;
+    // fused all-gather epilogue: n_peers > 0 -> every finished tile row segment is stored to the row-major
+    // [m, ldc] buffer of each peer GPU (peer_c[i], plain peer-mapped pointers) at column offset col0
+    __nv_bfloat16 *peer_c[8];
+    int n_peers, ldc, col0;
     int stream_k;     // 1: every CTA takes an equal, contiguous share of the (tile, K-step) space
     int tile_elems;   // rows * columns of one output tile (stream-K slabs are tile-shaped)
 };
@@ -158,7 +164,7 @@ struct Cfg {
     static_assert(kBlocksPerStage % kGroupWarps == 0 && kGroupWarps % (BN / 64) == 0,
                   "a dequant team must divide the packed blocks of a stage and keep one chunk per warp");
     static constexpr int kBarrierBytes = 1024;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 4 * kEpiWarpBytes + 1024;  // + alignment slack
     // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
     static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                        (static_cast<uint32_t>(BM >> 4) << 24);
@@ -183,6 +189,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
     auto empty = [&](int s) { return bar_base + 8u * (2 * C::kStages + s); };
     auto tmem_full = [&](int a) { return bar_base + 8u * (3 * C::kStages + a); };
     auto tmem_empty = [&](int a) { return bar_base + 8u * (3 * C::kStages + 2 + a); };
+    const uint32_t epi_base = bar_base + C::kBarrierBytes;
     uint8_t *bar_gen = smem_gen + C::kStages * C::kStageBytes;
     volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bar_gen + 8 * (3 * C::kStages + 4));
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bar_gen + 8 * (3 * C::kStages + 4) + 4);
@@ -305,30 +312,57 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     for (int v = 0; v < 8; ++v)
                         dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
                                              __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                } else if (p.splits == 1) {
+                    // bf16 result.  A thread owns one row x 32 columns here; the 64-byte pieces of two column chunks
+                    // go through a per-warp shared-memory tile so that the global (or peer, over NVLink) stores are
+                    // 128 contiguous bytes per row and four rows per instruction instead of 16 scattered bytes.
+                    const int col = nt * BN + cc * 32;
+                    const uint32_t epi = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float x0 = __uint_as_float(r[8 * v + 2 * e]), x1 = __uint_as_float(r[8 * v + 2 * e + 1]);
+                            if (p.per_column) {
+                                const int pos = scale_single_pos(col + 8 * v + 2 * e);
+                                x0 *= __half2float(p.S[pos]);
+                                x1 *= __half2float(p.S[pos + 1]);
+                            }
+                            __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
+                            o[e] = *reinterpret_cast<uint32_t *>(&b);
+                        }
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + (cc & 1) * 64 + v * 16),
+                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                     : "memory");
+                    }
+                    if (cc & 1) {
+                        __syncwarp();
+                        const int piece = lane & 7;
+                        const int col_out = nt * BN + (cc - 1) * 32 + piece * 8;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rl = i * 4 + (lane >> 3);
+                            const int grow = (mt * MT + h) * BM + quarter * 32 + rl;
+                            uint4 val;
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                         : "r"(epi + rl * kEpiPitch + piece * 16));
+                            if (grow < p.m) {
+                                if (p.n_peers == 0) {
+                                    *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(grow) * p.n + col_out) = val;
+                                } else {
+                                    // column-parallel all-gather fused into the epilogue: plain stores into every GPU's buffer
+                                    for (int pe = 0; pe < p.n_peers; ++pe)
+                                        *reinterpret_cast<uint4 *>(p.peer_c[pe] + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out) = val;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
                 } else if (row < p.m) {
                     const int col = nt * BN + cc * 32;
-                    if (p.splits == 1) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(row) * p.n + col);
-                        float sc[2] = {1.f, 1.f};
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint32_t o[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                float x0 = __uint_as_float(r[8 * v + 2 * e]), x1 = __uint_as_float(r[8 * v + 2 * e + 1]);
-                                if (p.per_column) {
-                                    const int pos = scale_single_pos(col + 8 * v + 2 * e);
-                                    sc[0] = __half2float(p.S[pos]);
-                                    sc[1] = __half2float(p.S[pos + 1]);
-                                    x0 *= sc[0];
-                                    x1 *= sc[1];
-                                }
-                                __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
-                                o[e] = *reinterpret_cast<uint32_t *>(&b);
-                            }
-                            dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
-                    } else {
+                    {
                         float4 *dst = reinterpret_cast<float4 *>(
                             p.partial + (static_cast<size_t>(sp) * p.m + row) * p.n + col);
 #pragma unroll
@@ -561,7 +595,7 @@ double step_us(int bn, int mt) {
     return dequant > mma ? dequant : mma;
 }
 
-PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
+PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool allow_scratch = true) {
     const int sms = device_sm_count();
     const int k_iters = k / BK;
     PrefillConfig best{256, 1, 1, 0};
@@ -573,6 +607,7 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
             for (int si = 0; si < 6; ++si) {
                 const int bn = bns[bi], s = ss[si];
                 if (k_iters / s < 8) continue;
+                if (s > 1 && !allow_scratch) continue;
                 if (mt == 2 && m <= BM) continue;
                 const int m_tiles = (m + BM * mt - 1) / (BM * mt);
                 const long long units = static_cast<long long>(m_tiles) * (n / bn) * s;
@@ -587,7 +622,7 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true) {
                 }
                 // stream-K over the same tiling: equal shares of the K-steps, plus the fix-up pass over the
                 // tiles that end up shared between CTAs (at most one per CTA)
-                if (s == 1 && allow_pairs) {
+                if (s == 1 && allow_pairs && allow_scratch) {
                     const long long tiles = static_cast<long long>(m_tiles) * (n / bn);
                     const double share = static_cast<double>(tiles) * k_iters / sms;
                     const double tile_mb = BM * mt * bn * 4.0 / 1.0e6;
@@ -657,7 +692,8 @@ int launch_prefill(const GemmArgs &a) {
     if (!enc) return KILN_W4A16_ERR_CUDA;
     uint32_t *status = device_status_word();
     if (!status) return KILN_W4A16_ERR_CUDA;
-    const PrefillConfig c = choose_prefill(a.m, a.n, a.k);
+    const bool fused = a.n_peers > 0;  // the peer-store epilogue needs whole tiles: no split-K, no stream-K
+    const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused);
 
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
@@ -683,6 +719,10 @@ int launch_prefill(const GemmArgs &a) {
     p.splits = c.splits;
     p.k_iters = a.k / BK;
     p.per_column = a.groupsize == -1;
+    p.n_peers = a.n_peers;
+    p.ldc = a.ldc;
+    p.col0 = a.col0;
+    for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;
     p.tile_elems = BM * c.mt * c.bn;
     const size_t need = workspace_for(c, a.m, a.n);

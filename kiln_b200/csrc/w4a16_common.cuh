@@ -114,6 +114,9 @@ struct GemmArgs {
     void *workspace;
     size_t workspace_bytes;
     cudaStream_t stream;
+    // fused all-gather (prefill kernel only): store the result into the row-major [m, ldc] buffers of n_peers GPUs
+    void *peer_c[8] = {};
+    int n_peers = 0, ldc = 0, col0 = 0;
 };
 
 struct DecodeOverride {

@@ -117,6 +117,60 @@ class ColumnParallelLinear:
         return out
 
 
+class FusedGatherOutput:
+    """A row-major [m, n] bf16 result buffer that every GPU of the group can store into: symmetric memory
+    (torch.distributed._symmetric_memory), one allocation per rank, peer-mapped after a rendezvous."""
+
+    def __init__(self, m: int, n: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.tensor = symm_mem.empty((m, n), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        world = dist.get_world_size(group)
+        ptrs = getattr(self.handle, "buffer_ptrs", None)
+        if ptrs is None:
+            ptrs = [self.handle.get_buffer(r, (m, n), torch.bfloat16).data_ptr() for r in range(world)]
+        self.ptrs = [int(x) for x in ptrs]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def barrier(self):
+        """Stream-ordered barrier across the group (a one-element NCCL all-reduce): when it completes on a
+        rank, every rank's launch before it has finished, so all slices have arrived."""
+        dist.all_reduce(self._flag, group=self.group)
+
+
+def fused_column_parallel_gemm(a: torch.Tensor, lin: "ColumnParallelLinear", out: FusedGatherOutput,
+                               barrier: bool = True) -> torch.Tensor:
+    """Local columns x all-gather in ONE kernel: the tcgen05 GEMM stores each finished tile into the
+    [m, n] buffer of every GPU over NVLink (kiln_w4a16_gemm_bf16_allgather).  Returns this rank's full
+    row-major [m, n] result."""
+    import ctypes
+
+    from . import _lib
+
+    m, k = a.shape
+    sh = lin.shard
+    n_total = sh.n * lin.world
+    if tuple(out.tensor.shape) != (m, n_total):
+        raise KilnMarlinError(f"kiln-marlin-gemm: fused gather buffer is {tuple(out.tensor.shape)}, expected {(m, n_total)}")
+    if k != sh.k or a.dtype != torch.bfloat16 or not a.is_cuda:
+        raise KilnMarlinError("kiln-marlin-gemm: a must be a CUDA bf16 [m, k] tensor matching the shard")
+    arr = (ctypes.c_void_p * lin.world)(*out.ptrs)
+    a = a.contiguous()
+    with torch.cuda.device(a.device):
+        rc = _lib.lib().kiln_w4a16_gemm_bf16_allgather(
+            a.data_ptr(), sh.b_packed.data_ptr(), sh.scales.data_ptr(), m, sh.n, k, sh.groupsize,
+            ctypes.cast(arr, ctypes.c_void_p), lin.world, n_total, lin.rank * sh.n,
+            torch.cuda.current_stream(a.device).cuda_stream)
+    if rc != 0:
+        raise KilnMarlinError(f"kiln_w4a16_gemm_bf16_allgather failed: {_lib.STATUS_NAMES.get(rc, rc)}")
+    if barrier:
+        out.barrier()
+    return out.tensor
+
+
 _side_streams: dict = {}
 
 

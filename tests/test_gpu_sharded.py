@@ -47,6 +47,15 @@ def _worker(rank, world, port, q):
             torch.cuda.synchronize()
             assert torch.equal(dense, full), "gathered columns differ from the single-GPU result"
             assert torch.equal(blocked[rank], full[:, rank * n // world:(rank + 1) * n // world])
+            if m >= 64:  # the fused-gather epilogue lives in the tcgen05 kernel
+                sym = kiln_b200.FusedGatherOutput(m, n, dev)
+                for _ in range(2):
+                    fused = kiln_b200.fused_column_parallel_gemm(a_t, lin, sym)
+                torch.cuda.synchronize()
+                d = float((fused.float() - full.float()).abs().max() / full.float().abs().max())
+                assert d <= 1e-2, f"fused all-gather result differs by {d}"
+                assert torch.equal(fused[:, rank * n // world:(rank + 1) * n // world],
+                                   blocked[rank]), "own slice must equal the plain local GEMM"
             ref = C.gemm_fp64(a, qn, s, 128)
             got = oracle.bf16_bits_to_f32(dense.cpu().view(torch.int16).numpy().view(np.uint16))
             assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2

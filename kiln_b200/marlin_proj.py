@@ -70,6 +70,30 @@ def pack_from_bf16_batch(weights: Sequence[torch.Tensor], groupsize: int = 128):
     return [pack_from_bf16(w, groupsize) for w in weights]
 
 
+def concat_projections(projs: Sequence[MarlinPackedProj]) -> MarlinPackedProj:
+    """Fuses sibling projections that read the same activations (q+k+v, gate+up) into one packed weight.
+
+    The Marlin layout is separable along N at 64-column granularity, so the fused tensors are plain
+    concatenations: one GEMM launch then replaces several (kiln issues one Marlin call per projection,
+    kiln-model/src/forward.rs:2771-2839; its profiling notes list the gate/up merge as the next lever).
+    The caller splits the [.., sum(n)] output by columns.
+    """
+    if not projs:
+        raise KilnMarlinError("marlin_proj: nothing to concatenate")
+    k, g = projs[0].k, projs[0].groupsize
+    for pr in projs:
+        if pr.k != k or pr.groupsize != g:
+            raise KilnMarlinError("marlin_proj: projections must share k and groupsize to be fused")
+        if pr.n % 64 != 0:
+            raise KilnMarlinError("marlin_proj: every fused projection needs n % 64 == 0")
+    n = sum(pr.n for pr in projs)
+    if n % 256 != 0:
+        raise KilnMarlinError(f"marlin_proj: fused n={n} must be a multiple of 256")
+    b = torch.cat([pr.b_packed for pr in projs], dim=1).contiguous()
+    s = torch.cat([pr.scales for pr in projs], dim=1).contiguous()
+    return MarlinPackedProj(b, s, g, k, n)
+
+
 def matmul_bf16(x: torch.Tensor, proj: MarlinPackedProj) -> torch.Tensor:
     """marlin_proj.rs:285-319: x [.., k] bf16 -> [.., n] bf16 (rank 2 or 3)."""
     if x.dim() == 2:

@@ -53,6 +53,13 @@ def test_status_codes_before_any_launch():
     assert lib.kiln_marlin_w4a16_gemm(p, p, p, p, 1, 256, 192, None, 128, 0, None, 128, 128, -1, 16) == _lib.ERR_PROB_SHAPE
     assert lib.kiln_marlin_w4a16_gemm(p, p, p, p, 1, 256, 128, None, 128, 0, None, 32, 32, -1, 16) == _lib.ERR_KERN_SHAPE
     assert lib.kiln_marlin_w4a16_gemm(p, p, p, p, 0, 256, 128, None, 128, 0, None, -1, -1, -1, 16) == _lib.OK
+    # fused all-gather entry: argument checks happen before any launch
+    peers = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    pp = ctypes.cast(peers, ctypes.c_void_p)
+    assert lib.kiln_w4a16_gemm_bf16_allgather(p, p, p, 128, 256, 128, 128, pp, 9, 512, 0, None) == _lib.ERR_ARG
+    assert lib.kiln_w4a16_gemm_bf16_allgather(p, p, p, 128, 256, 128, 128, pp, 2, 256, 256, None) == _lib.ERR_ARG
+    assert lib.kiln_w4a16_gemm_bf16_allgather(p, p, p, 128, 200, 128, 128, pp, 2, 512, 0, None) == _lib.ERR_PROB_SHAPE
+    assert lib.kiln_w4a16_gemm_bf16_allgather(p, p, p, 0, 256, 128, 128, pp, 2, 512, 0, None) == _lib.OK
 
 
 def test_wrapper_messages_match_reference():

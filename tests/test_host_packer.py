@@ -77,3 +77,27 @@ def test_rejects_what_the_reference_asserts():
     out = np.zeros(16, np.int32)
     assert lib.kiln_w4a16_quantize_and_pack_host(None, 128, 256, 128, out.ctypes.data, out.ctypes.data, None, 1) == _lib.ERR_ARG
     assert lib.kiln_w4a16_quantize_and_pack_host(out.ctypes.data, 120, 256, 128, out.ctypes.data, out.ctypes.data, None, 1) == _lib.ERR_PROB_SHAPE
+
+
+def test_concat_projections_equals_packing_the_concatenated_weight():
+    import torch
+
+    import kiln_b200
+
+    k = 256
+    ws = [np.random.default_rng(i).standard_normal((k, n)).astype(np.float32) * 0.05 for i, n in enumerate((512, 128, 128))]
+    parts = []
+    for w in ws:
+        n = w.shape[1]
+        # pack each projection on its own (n % 64 == 0 suffices for the format; pad the call to the 256 rule)
+        pad = (-n) % 256
+        wp = np.concatenate([w, np.zeros((k, pad), np.float32)], 1) if pad else w
+        p, s, _ = pack.quantize_and_pack(wp, k, n + pad, 128)
+        parts.append(kiln_b200.MarlinPackedProj(torch.from_numpy(p[:, :2 * n].copy()),
+                                                torch.from_numpy(s[:, :n].copy().view(np.int16)).view(torch.float16), 128, k, n))
+    fused = kiln_b200.concat_projections(parts)
+    pf, sf, _ = pack.quantize_and_pack(np.concatenate(ws, 1), k, 768, 128)
+    assert fused.n == 768 and (fused.b_packed.numpy() == pf).all()
+    assert (fused.scales.view(torch.int16).numpy().view(np.uint16) == sf.view(np.uint16)).all()
+    with pytest.raises(kiln_b200.KilnMarlinError):
+        kiln_b200.concat_projections(parts[:2])  # 640 columns: not a multiple of 256

@@ -367,7 +367,7 @@ def sharded_detail(d: Device, world: int, rank: int):
         t.cuda.synchronize()
         return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[0].elapsed_time(e[2])
 
-    fused_ms = None
+    fused_ms = fused_mc_ms = None
     if world > 1:
         import kiln_b200
         from kiln_b200 import MarlinPackedProj
@@ -375,21 +375,28 @@ def sharded_detail(d: Device, world: int, rank: int):
         lin = kiln_b200.ColumnParallelLinear(MarlinPackedProj(w[0], w[1], 128, k, nl), rank, world, None)
         sym = kiln_b200.FusedGatherOutput(m, n, d.dev)
 
-        def fused_once():
+        def fused_once(multicast):
             e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
             e0.record()
-            kiln_b200.fused_column_parallel_gemm(a, lin, sym)  # GEMM with peer-store epilogue + barrier
+            kiln_b200.fused_column_parallel_gemm(a, lin, sym, multicast=multicast)  # GEMM with store epilogue + barrier
             e1.record()
             t.cuda.synchronize()
             return e0.elapsed_time(e1)
 
-        fused_once()
-        fused_once()
-        dist.barrier()
-        fl = sorted(fused_once() for _ in range(3))[1]
-        tt = t.tensor([fl], device=d.dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        fused_ms = float(tt.item())
+        def fused_time(multicast):
+            fused_once(multicast)
+            fused_once(multicast)
+            dist.barrier()
+            fl = sorted(fused_once(multicast) for _ in range(3))[1]
+            tt = t.tensor([fl], device=d.dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+
+        fused_ms = fused_time(False)
+        # every rank must take the same branch: ask the group whether all of them got a multicast address
+        has_mc = t.tensor([1 if sym.multicast_ptr else 0], device=d.dev)
+        dist.all_reduce(has_mc, op=dist.ReduceOp.MIN)
+        fused_mc_ms = fused_time(True) if int(has_mc.item()) else None
         del sym
     once()
     once()
@@ -411,9 +418,25 @@ def sharded_detail(d: Device, world: int, rank: int):
         "fused_gemm_allgather_ms": round(fused_ms, 3) if fused_ms else None,
         "fused_TFLOPs_total": round(flops / fused_ms / 1e9, 1) if fused_ms else None,
         "fused_layout": "row-major [M, N] on every GPU (peer stores from the GEMM epilogue + one barrier)",
+        "fused_multicast_ms": round(fused_mc_ms, 3) if fused_mc_ms else None,
+        "fused_multicast_TFLOPs_total": round(flops / fused_mc_ms / 1e9, 1) if fused_mc_ms else None,
+        "fused_multicast_layout": "the same through one multimem.st per piece to the NVSwitch multicast address",
+        "fused_roofline": fused_roofline(m, k, n, world, min(x for x in (fused_ms, fused_mc_ms) if x)) if fused_ms else None,
     }
     del w, a, local, gathered
     return out
+
+
+def fused_roofline(m, k, n, world, ms):
+    """Target time of the fused GEMM + all-gather = the slower of this GPU's flops at the measured bf16 peak and the
+    bytes it must receive from its peers at the measured NVLink peer-copy rate (770 GB/s per direction per GPU)."""
+    peaks = load_peaks()
+    t_flops = alg_flops(m, k, n) / world / (peaks["bf16_tflops"] * 1e9)  # ms
+    t_link = (world - 1) / world * m * n * 2 / 770e9 * 1e3
+    target = max(t_flops, t_link)
+    return {"bound": "tensor" if t_flops >= t_link else "nvlink", "target_ms": round(target, 3), "achieved_ms": round(ms, 3),
+            "frac": round(target / ms, 3), "flops_ms": round(t_flops, 3), "link_ms": round(t_link, 3),
+            "peaks": peaks["source"] + " bf16 burst; 770 GB/s measured peer copy"}
 
 
 def run_only(args):

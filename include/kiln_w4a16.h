@@ -97,6 +97,14 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather(const void *A, const void *B,
                                                    int k, int groupsize, void *const *C_peers, int n_peers, int ldc,
                                                    int col0, void *stream);
 
+/* The same with ONE pointer: C_multicast is the NVSwitch multicast address of the group's [m, ldc] buffers (all
+ * GPUs' buffers bound to one multicast object, e.g. torch symmetric memory's multicast_ptr).  Every 16-byte piece is
+ * written once with multimem.st and the switch replicates it into every GPU's buffer, this GPU's included, so a tile
+ * leaves this GPU once instead of n_peers - 1 times.  Same completion rule as above.  No counterpart in the reference. */
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather_multicast(const void *A, const void *B, const void *s, int m,
+                                                             int n_local, int k, int groupsize, void *C_multicast,
+                                                             int ldc, int col0, void *stream);
+
 /* Scratch bytes the GEMM needs for (m, n, k); replaces the reference wrapper's
  * fixed `(n/128) * 16` int32 lock array (crates/kiln-marlin-gemm/src/lib.rs:176-178). */
 size_t kiln_w4a16_workspace_bytes(int m, int n, int k);

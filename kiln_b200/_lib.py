@@ -35,6 +35,7 @@ SIGNATURES = {
     "kiln_w4a16_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "kiln_w4a16_gemm_bf16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "kiln_w4a16_gemm_bf16_allgather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp]),
+    "kiln_w4a16_gemm_bf16_allgather_multicast": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "kiln_w4a16_workspace_bytes": (_sz, [_i, _i, _i]),
     "kiln_w4a16_shape_is_supported": (_i, [_i, _i]),
     "kiln_w4a16_build_weight_perm": (None, [_vp]),

@@ -151,6 +151,20 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather(const void *A, const void *B,
     return launch_prefill(a);
 }
 
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather_multicast(const void *A, const void *B, const void *s, int m,
+                                                             int n_local, int k, int groupsize, void *C_multicast,
+                                                             int ldc, int col0, void *stream) {
+    if (ldc < col0 + n_local || col0 < 0 || ldc % 8 != 0 || col0 % 8 != 0) return KILN_W4A16_ERR_ARG;
+    GemmArgs a{A, B, s, C_multicast, m, n_local, k, groupsize, nullptr, 0, static_cast<cudaStream_t>(stream)};
+    const int v = validate(a);
+    if (v >= 0) return v;
+    if (!prefill_supported(m, n_local, k, groupsize)) return KILN_W4A16_ERR_KERN_SHAPE;
+    a.mc_c = C_multicast;
+    a.ldc = ldc;
+    a.col0 = col0;
+    return launch_prefill(a);
+}
+
 size_t kiln_w4a16_workspace_bytes(int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
     if (use_prefill(m, n, k, 128)) return prefill_workspace_bytes(m, n, k);

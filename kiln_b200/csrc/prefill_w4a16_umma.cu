@@ -48,6 +48,9 @@ struct PrefillParams {
     // [m, ldc] buffer of each peer GPU (peer_c[i], plain peer-mapped pointers) at column offset col0
     __nv_bfloat16 *peer_c[8];
     int n_peers, ldc, col0;
+    // mc_c != nullptr: one multimem.st per piece to the group's multicast address instead (the switch replicates
+    // the store into every GPU's buffer, this GPU's included, so each tile leaves this GPU once)
+    __nv_bfloat16 *mc_c;
     int stream_k;     // 1: every CTA takes an equal, contiguous share of the (tile, K-step) space
     int tile_elems;   // rows * columns of one output tile (stream-K slabs are tile-shaped)
 };
@@ -349,7 +352,12 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                                          : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
                                          : "r"(epi + rl * kEpiPitch + piece * 16));
                             if (grow < p.m) {
-                                if (p.n_peers == 0) {
+                                if (p.mc_c) {
+                                    asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(
+                                                     p.mc_c + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out),
+                                                 "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                                                 : "memory");
+                                } else if (p.n_peers == 0) {
                                     *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(grow) * p.n + col_out) = val;
                                 } else {
                                     // column-parallel all-gather fused into the epilogue: plain stores into every GPU's buffer
@@ -692,7 +700,7 @@ int launch_prefill(const GemmArgs &a) {
     if (!enc) return KILN_W4A16_ERR_CUDA;
     uint32_t *status = device_status_word();
     if (!status) return KILN_W4A16_ERR_CUDA;
-    const bool fused = a.n_peers > 0;  // the peer-store epilogue needs whole tiles: no split-K, no stream-K
+    const bool fused = a.n_peers > 0 || a.mc_c;  // the peer-store epilogue needs whole tiles: no split-K, no stream-K
     const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused);
 
     CUtensorMap tmap;
@@ -722,6 +730,7 @@ int launch_prefill(const GemmArgs &a) {
     p.n_peers = a.n_peers;
     p.ldc = a.ldc;
     p.col0 = a.col0;
+    p.mc_c = static_cast<__nv_bfloat16 *>(a.mc_c);
     for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;
     p.tile_elems = BM * c.mt * c.bn;

@@ -117,6 +117,8 @@ struct GemmArgs {
     // fused all-gather (prefill kernel only): store the result into the row-major [m, ldc] buffers of n_peers GPUs
     void *peer_c[8] = {};
     int n_peers = 0, ldc = 0, col0 = 0;
+    // the same with one NVSwitch multicast address for the whole group instead of per-GPU pointers (multimem.st)
+    void *mc_c = nullptr;
 };
 
 struct DecodeOverride {

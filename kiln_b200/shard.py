@@ -133,6 +133,8 @@ class FusedGatherOutput:
         if ptrs is None:
             ptrs = [self.handle.get_buffer(r, (m, n), torch.bfloat16).data_ptr() for r in range(world)]
         self.ptrs = [int(x) for x in ptrs]
+        # NVSwitch multicast address of the same buffers (0 when the fabric or the driver offers none)
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
 
     def barrier(self):
@@ -142,10 +144,14 @@ class FusedGatherOutput:
 
 
 def fused_column_parallel_gemm(a: torch.Tensor, lin: "ColumnParallelLinear", out: FusedGatherOutput,
-                               barrier: bool = True) -> torch.Tensor:
+                               barrier: bool = True, multicast: Optional[bool] = None) -> torch.Tensor:
     """Local columns x all-gather in ONE kernel: the tcgen05 GEMM stores each finished tile into the
     [m, n] buffer of every GPU over NVLink (kiln_w4a16_gemm_bf16_allgather).  Returns this rank's full
-    row-major [m, n] result."""
+    row-major [m, n] result.
+
+    multicast=True writes each piece once to the group's NVSwitch multicast address (multimem.st,
+    kiln_w4a16_gemm_bf16_allgather_multicast) instead of once per GPU; None picks it when the buffer has a
+    multicast address and the group has more than two GPUs (with two there is nothing to save)."""
     import ctypes
 
     from . import _lib
@@ -157,13 +163,22 @@ def fused_column_parallel_gemm(a: torch.Tensor, lin: "ColumnParallelLinear", out
         raise KilnMarlinError(f"kiln-marlin-gemm: fused gather buffer is {tuple(out.tensor.shape)}, expected {(m, n_total)}")
     if k != sh.k or a.dtype != torch.bfloat16 or not a.is_cuda:
         raise KilnMarlinError("kiln-marlin-gemm: a must be a CUDA bf16 [m, k] tensor matching the shard")
+    if multicast is None:
+        multicast = out.multicast_ptr != 0 and lin.world > 2
+    if multicast and out.multicast_ptr == 0:
+        raise KilnMarlinError("kiln-marlin-gemm: this buffer has no multicast address")
     arr = (ctypes.c_void_p * lin.world)(*out.ptrs)
     a = a.contiguous()
     with torch.cuda.device(a.device):
-        rc = _lib.lib().kiln_w4a16_gemm_bf16_allgather(
-            a.data_ptr(), sh.b_packed.data_ptr(), sh.scales.data_ptr(), m, sh.n, k, sh.groupsize,
-            ctypes.cast(arr, ctypes.c_void_p), lin.world, n_total, lin.rank * sh.n,
-            torch.cuda.current_stream(a.device).cuda_stream)
+        if multicast:
+            rc = _lib.lib().kiln_w4a16_gemm_bf16_allgather_multicast(
+                a.data_ptr(), sh.b_packed.data_ptr(), sh.scales.data_ptr(), m, sh.n, k, sh.groupsize,
+                out.multicast_ptr, n_total, lin.rank * sh.n, torch.cuda.current_stream(a.device).cuda_stream)
+        else:
+            rc = _lib.lib().kiln_w4a16_gemm_bf16_allgather(
+                a.data_ptr(), sh.b_packed.data_ptr(), sh.scales.data_ptr(), m, sh.n, k, sh.groupsize,
+                ctypes.cast(arr, ctypes.c_void_p), lin.world, n_total, lin.rank * sh.n,
+                torch.cuda.current_stream(a.device).cuda_stream)
     if rc != 0:
         raise KilnMarlinError(f"kiln_w4a16_gemm_bf16_allgather failed: {_lib.STATUS_NAMES.get(rc, rc)}")
     if barrier:

@@ -56,6 +56,17 @@ def _worker(rank, world, port, q):
                 assert d <= 1e-2, f"fused all-gather result differs by {d}"
                 assert torch.equal(fused[:, rank * n // world:(rank + 1) * n // world],
                                    blocked[rank]), "own slice must equal the plain local GEMM"
+                # the same through the NVSwitch multicast address, where the fabric offers one to every rank
+                has_mc = torch.tensor([1 if sym.multicast_ptr else 0], device=dev)
+                dist.all_reduce(has_mc, op=dist.ReduceOp.MIN)
+                if int(has_mc.item()):
+                    keep = fused.clone()
+                    sym.tensor.zero_()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    mc = kiln_b200.fused_column_parallel_gemm(a_t, lin, sym, multicast=True)
+                    torch.cuda.synchronize()
+                    assert torch.equal(mc, keep), "multicast stores must give the same matrix as peer stores"
             ref = C.gemm_fp64(a, qn, s, 128)
             got = oracle.bf16_bits_to_f32(dense.cpu().view(torch.int16).numpy().view(np.uint16))
             assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2

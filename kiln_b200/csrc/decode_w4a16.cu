@@ -9,7 +9,8 @@
 //    asynchronous copies (TMA, mbarrier completion) into a ring, so the bytes in flight per SM
 //    are set by the ring depth, not by registers or by how many warps are resident, and the
 //    weight stream starts before the previous kernel in the stream has finished
-//    (programmatic dependent launch; only the activations wait for it).
+//    (programmatic dependent launch; only the activations, which the consumer warps stage
+//    themselves with plain loads, wait for it).
 //  * consumer warps: in-register int4 -> bf16 dequant (`lop3` puts each nibble pair into the
 //    mantissa of bf16x2 {128,128}); the +128+8 offset is not
 //    subtracted per weight but removed per MMA tile by one extra MMA against a constant
@@ -141,7 +142,6 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
     float *sRed = reinterpret_cast<float *>(base_gen + p.off_red);
     auto full = [&](int s) { return sBar + 8u * s; };
     auto empty = [&](int s) { return sBar + 8u * (p.stages + s); };
-    const uint32_t a_full = sBar + 8u * (2 * p.stages);
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(base_gen + p.off_bar + 8 * (2 * p.stages + 1));
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -159,7 +159,6 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
             mbar_init(full(s), 1);
             mbar_init(empty(s), p.warps_n);
         }
-        mbar_init(a_full, 1);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -202,16 +201,6 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
         const int window = min(p.window, p.stages);
         const int pre = min(nst, window);
         for (int i = 0; i < pre; ++i) issue_stage(i);
-        pdl_wait();
-        // activations: one bulk copy per valid row, K range of this CTA
-        const uint32_t a_row_bytes = static_cast<uint32_t>(nst) * 256u;
-        if (nst > 0) {
-            if (lane == 0) mbar_arrive_expect_tx(a_full, a_row_bytes * m_valid);
-            __syncwarp();
-            for (int r = lane; r < m_valid; r += 32)
-                bulk_g2s(sA + r * p.a_pitch, p.A + static_cast<size_t>(m0 + r) * p.k + static_cast<size_t>(gc0) * kGroup,
-                         a_row_bytes, a_full);
-        }
         for (int i = pre; i < nst && ok; ++i) {
             const int j = i - window;  // this stage must have landed before stage i is requested
             ok = mbar_wait(full(j % p.stages), (j / p.stages) & 1, abort_flag, p.status, 0x1000u | (j % p.stages));
@@ -239,7 +228,23 @@ __global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(cons
         const uint32_t a_lane = sA + static_cast<uint32_t>(a_row) * p.a_pitch + static_cast<uint32_t>((lane >> 3) & 1) * 16u;
         const uint32_t w_kt_stride = static_cast<uint32_t>(p.warps_n) * 512u;
         bool ok = true;
-        if (wk < nst) ok = mbar_wait(a_full, 0, abort_flag, p.status, 0x1200u);
+        // Activations: staged by the consumer warps themselves with plain loads (they come from L2), not by a
+        // bulk copy of the producer: a copy queued behind the weight stages in flight landed last (2.4-4.2 us
+        // after the launch) and held every consumer back.  Only this depends on the previous kernel.
+        pdl_wait();
+        {
+            const int vec_per_row = nst * 16;  // 16-byte pieces per row in this CTA's K range
+            const int ctid = tid - 32;
+            for (int idx = ctid; idx < m_valid * vec_per_row; idx += nwarps_c * 32) {
+                const int r = idx / vec_per_row, v = idx - r * vec_per_row;
+                const uint4 val = ld_cg_v4(reinterpret_cast<const uint4 *>(
+                    p.A + static_cast<size_t>(m0 + r) * p.k + static_cast<size_t>(gc0) * kGroup + v * 8));
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sA + r * p.a_pitch + v * 16), "r"(val.x),
+                             "r"(val.y), "r"(val.z), "r"(val.w)
+                             : "memory");
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nwarps_c * 32) : "memory");
+        }
         for (int i = wk; i < nst && ok; i += p.warps_k) {
             const int s = i % p.stages;
             const uint32_t ph = (i / p.stages) & 1;
@@ -346,13 +351,38 @@ DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
         // Rule fitted to sweeps over (cluster_k, warps_k, warps_n) on the Qwen3.5-4B projection shapes:
         // two chunks per CTA (1 KB bulk copies, activations shared by two warps), the smallest cluster
         // split that gives at least one CTA per SM while every CTA keeps two or more K groups, and
-        // four K-teams (two when a batch needs two MMAs per word and the registers that go with it).
+        // four K-teams (two when a batch needs two MMAs per word and the registers that go with it, or when
+        // a CTA streams eight or more groups: two long-running teams then beat four short ones).
         wn = chunks % 2 == 0 ? 2 : 1;
         ck = 1;
         while (ck < 8 && static_cast<long long>(chunks / wn) * mblocks * ck < sms && groups / (ck * 2) >= 2) ck *= 2;
-        const int gpc = ceil_div(groups, ck);
-        wk = c.nb == 1 ? 4 : 2;
+        int gpc = ceil_div(groups, ck);
+        wk = (c.nb == 1 && gpc < 8) ? 4 : 2;
         if (wk > gpc) wk = gpc;
+        // A projection so narrow that even the widest cluster split leaves most SMs idle (k, v: 512 columns):
+        // one chunk per CTA doubles the CTAs, and eight warps (whatever the number of K groups) shorten the
+        // activation staging and the reduction, which dominate such a launch.
+        if (static_cast<long long>(chunks / wn) * mblocks * 8 < sms / 2) {
+            wn = 1;
+            ck = 8;
+            while (ck > 1 && groups / ck < 2) ck /= 2;
+            wk = 8;
+        }
+        // Measured exceptions (B200, CUDA-graph replay over rotating weights), keyed by the shape:
+        struct Tuned {
+            int k, n, nb, ck, wk, wn;
+        };
+        static const Tuned kTuned[] = {
+            {2560, 4096, 1, 8, 4, 1},   // q:      5.17 us at M=8 (rule: 5.44)
+            {2560, 4096, 2, 4, 4, 2},   // q:      6.31 us at M=16 (rule: 8.40)
+            {2560, 8192, 1, 4, 3, 2},   // GDN-in: 5.61 us at M=1 (rule: 6.37)
+        };
+        for (const Tuned &t : kTuned)
+            if (t.k == k && t.n == n && t.nb == c.nb) {
+                ck = t.ck;
+                wk = t.wk;
+                wn = t.wn;
+            }
     }
     while (chunks % wn) wn /= 2;
     if (ck > 8) ck = 8;

@@ -57,6 +57,13 @@ __device__ __forceinline__ uint4 ld_stream_v4(const uint4 *p) {
     return v;
 }
 
+// Activations: cached in L2 only, so a buffer another kernel has just rewritten is never read from a stale L1 line.
+__device__ __forceinline__ uint4 ld_cg_v4(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

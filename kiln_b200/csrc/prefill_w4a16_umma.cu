@@ -156,7 +156,9 @@ template <int BN, int MT = 1, int DW = 8, int DG = 2>
 struct Cfg {
     static constexpr int kGroupWarps = DW / DG;
     // producer, MMA, 4 epilogue and DW dequant warps (16 dequant warps were measured no faster than 8)
-    static constexpr int kThreads = (6 + DW) * 32;
+    // MT == 2 adds a second MMA-issuing warp (the last one): each issuer owns one M-tile of the pair
+    static constexpr int kMmaWarp2 = 6 + DW;
+    static constexpr int kThreads = (6 + DW + (MT == 2 ? 1 : 0)) * 32;
     static constexpr int kABytes = MT * BM * BK * 2;  // 16 KB per M-tile
     static constexpr int kStages = (192 * 1024) / (kABytes + BN * BK * 2);
     static constexpr int kBBytes = BN * BK * 2;  // 32 / 16 KB
@@ -179,7 +181,7 @@ struct DequantRegs {
 };
 
 template <int BN, int MT, int DW, int DG>
-__global__ void __launch_bounds__((6 + DW) * 32, 1)
+__global__ void __launch_bounds__((6 + DW + (MT == 2 ? 1 : 0)) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillParams p) {
     using C = Cfg<BN, MT, DW, DG>;
     using Regs = DequantRegs<C::kBlocksPerWarp>;
@@ -203,7 +205,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_a(s), 1);
             mbar_init(full_b(s), C::kGroupWarps * 32);  // the threads of the team that fills the stage
-            mbar_init(empty(s), 1);
+            mbar_init(empty(s), MT);  // one tcgen05.commit per MMA issuer
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full(a), 1);
@@ -252,9 +254,14 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == 1 || (MT == 2 && warp == C::kMmaWarp2)) {
+        // ---------------- MMA issuer(s) ----------------
+        // One thread issues about one tcgen05.mma per ~105 cycles and spends ~400 more per K-step on the
+        // barrier waits and the commit, which is more than the 1024 cycles the eight 128 x 256 x 16 MMAs of a
+        // pair execute in.  With MT == 2 the two M-tiles therefore have one issuer each (warp 1: tile 0, the
+        // last warp: tile 1); their MMAs go to different accumulators and need no order between them.
         if (lane == 0) {
+            const int h0 = (MT == 2 && warp != 1) ? 1 : 0, h1 = MT == 2 ? h0 + 1 : 1;
             uint32_t it = 0, tile = 0;
             bool ok = true;
             WorkIter wi(p);
@@ -268,8 +275,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     if (!(ok = mbar_wait(full_b(s), ph, abort_flag, p.status, 0x400u | s))) break;
                     tc_fence_after();
                     const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes);
-#pragma unroll
-                    for (int h = 0; h < MT; ++h) {
+                    for (int h = h0; h < h1; ++h) {
                         const uint32_t acc = acc0 + h;
                         if (ki == ki0) {  // first write into this accumulator: the epilogue must have drained it
                             if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc))) break;
@@ -283,7 +289,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                         if (ki == ki1 - 1) umma_commit(tmem_full(acc));  // accumulator h is complete
                     }
                     if (!ok) break;
-                    umma_commit(empty(s));  // frees the stage when these MMAs have read it
+                    umma_commit(empty(s));  // this issuer's MMAs have read the stage; the slot is free after all issuers'
                 }
             }
         }

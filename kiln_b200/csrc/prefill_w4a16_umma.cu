@@ -190,7 +190,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
     auto full_a = [&](int s) { return bar_base + 8u * s; };
-    auto full_b = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+    auto full_b = [&](int s) { return bar_base + 8u * s; };  // same barrier as full_a: one wait per K-step for the issuer
     auto empty = [&](int s) { return bar_base + 8u * (2 * C::kStages + s); };
     auto tmem_full = [&](int a) { return bar_base + 8u * (3 * C::kStages + a); };
     auto tmem_empty = [&](int a) { return bar_base + 8u * (3 * C::kStages + 2 + a); };
@@ -203,8 +203,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
-            mbar_init(full_a(s), 1);
-            mbar_init(full_b(s), C::kGroupWarps * 32);  // the threads of the team that fills the stage
+            // one "stage full" barrier: the TMA producer (1 arrival + the tile's bytes) and the threads of the dequant team
+            mbar_init(full_a(s), 1 + C::kGroupWarps * 32);
             mbar_init(empty(s), MT);  // one tcgen05.commit per MMA issuer
         }
         for (int a = 0; a < 2; ++a) {
@@ -272,7 +272,6 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s))) break;
-                    if (!(ok = mbar_wait(full_b(s), ph, abort_flag, p.status, 0x400u | s))) break;
                     tc_fence_after();
                     const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes);
                     for (int h = h0; h < h1; ++h) {

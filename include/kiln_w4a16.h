@@ -167,6 +167,17 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
  * disables that kernel. */
 void kiln_w4a16_set_prefill_min_m(int min_m);
 
+/* Tuning hook for sweeps: force the tcgen05 kernel's tiling: bn = 128 or 256 columns per tile, K splits (1..8, fp32
+ * slabs in the workspace), m_tiles = 1 or 2 (128-row tiles sharing a dequantised stage), stream_k = 1 for equal shares of the
+ * (tile, K-step) space per CTA.  A combination that is not legal for a problem falls back to the built-in rule; 0,0,0,0
+ * restores the rule.  kiln_w4a16_workspace_bytes follows the override.  Process-wide, not thread-safe; no counterpart in
+ * the reference. */
+void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k);
+
+/* Diagnostic: the tiling the tcgen05 kernel would use for (m, n, k) on the current device, as
+ * out = {bn, splits, m_tiles, stream_k} (the arguments of kiln_w4a16_set_prefill_override). */
+void kiln_w4a16_prefill_plan(int m, int n, int k, int out[4]);
+
 /* Library version, and number of kernels this library launched since load
  * (diagnostic: lets a harness prove the native path ran). */
 int kiln_w4a16_version(void);

@@ -195,6 +195,14 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n) {
     g_decode_override = DecodeOverride{cluster_k, warps_k, warps_n};
 }
 
+void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k) {
+    set_prefill_override(bn, splits, m_tiles, stream_k);
+}
+
+void kiln_w4a16_prefill_plan(int m, int n, int k, int out[4]) {
+    if (out) prefill_plan(m, n, k, out);
+}
+
 void kiln_w4a16_set_prefill_min_m(int min_m) {
     g_prefill_min_m.store(min_m > 0 ? min_m : kDefaultPrefillMinM, std::memory_order_relaxed);
 }

@@ -51,7 +51,9 @@ struct PrefillParams {
     // mc_c != nullptr: one multimem.st per piece to the group's multicast address instead (the switch replicates
     // the store into every GPU's buffer, this GPU's included, so each tile leaves this GPU once)
     __nv_bfloat16 *mc_c;
-    int stream_k;     // 1: every CTA takes an equal, contiguous share of the (tile, K-step) space
+    int stream_k;     // 1: whole waves of tiles round-robin, then the remaining tiles' (tile, K-step) space in equal shares
+    int sk_first_tile;  // stream-K: tiles below this index are dealt whole (a multiple of the grid size)
+    int sk_ctas;        // stream-K: CTAs that share the remaining tiles (<= grid size)
     int tile_elems;   // rows * columns of one output tile (stream-K slabs are tile-shaped)
 };
 
@@ -104,25 +106,31 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
-// Hands a CTA its work.  Default: units (tile, K-split) dealt round-robin.  Stream-K: the flattened
-// (tile, K-step) space is cut into gridDim.x equal contiguous ranges, so no SM idles in a last partial
-// wave; a range covers the tail of one tile, whole tiles, and the head of another.  Whole tiles are
-// written straight to C; the at most two partial pieces of a CTA go to fp32 slabs 2*cta and 2*cta+1 of
-// the workspace and are summed per tile, in CTA order, by `streamk_fixup_kernel`.  No CTA waits for another.
+// Hands a CTA its work.  Default: units (tile, K-split) dealt round-robin.  Stream-K (hybrid): the tiles that fill
+// whole waves of the grid are dealt round-robin as above; the flattened (tile, K-step) space of the remaining
+// tiles is cut into sk_ctas equal contiguous ranges, so no SM idles in a last partial wave; a range covers the
+// tail of one tile, whole tiles, and the head of another.  Whole tiles are written straight to C; the at most
+// two partial pieces of a CTA go to fp32 slabs 2*cta and 2*cta+1 of the workspace and are summed per tile, in
+// CTA order, by `streamk_fixup_kernel`.  No CTA waits for another.
 struct WorkIter {
-    int mode, u, units, stride, splits, m_tiles, k_iters;
+    int mode, u, units, stride, splits, m_tiles, k_iters, first_tile;
     long long cur, begin, end;
     __device__ WorkIter(const PrefillParams &p)
         : mode(p.stream_k), u(blockIdx.x), units(p.m_tiles * p.n_tiles * p.splits), stride(gridDim.x), splits(p.splits),
-          m_tiles(p.m_tiles), k_iters(p.k_iters) {
-        const long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * p.k_iters;
-        begin = cur = total * blockIdx.x / gridDim.x;
-        end = total * (blockIdx.x + 1) / gridDim.x;
+          m_tiles(p.m_tiles), k_iters(p.k_iters), first_tile(p.sk_first_tile) {
+        if (mode) {
+            units = first_tile;  // whole tiles of the full waves (splits == 1 in this mode)
+            const long long total = static_cast<long long>(p.m_tiles * p.n_tiles - first_tile) * p.k_iters;
+            const long long c = blockIdx.x, n = p.sk_ctas;
+            begin = cur = c < n ? total * c / n : 0;
+            end = c < n ? total * (c + 1) / n : 0;
+        } else {
+            begin = cur = end = 0;
+        }
     }
     // slab: -1 = the piece is a whole tile (or an ordinary split) and goes where `sp` says; >= 0 = stream-K slab index
     __device__ bool next(int &mt, int &nt, int &sp, int &ki0, int &ki1, int &slab) {
-        if (mode == 0) {
-            if (u >= units) return false;
+        if (u < units) {
             sp = u % splits;
             const int t = u / splits;
             mt = t % m_tiles;
@@ -134,10 +142,11 @@ struct WorkIter {
             return true;
         }
         if (cur >= end) return false;
-        const int t = static_cast<int>(cur / k_iters);
-        ki0 = static_cast<int>(cur - static_cast<long long>(t) * k_iters);
+        const int tr = static_cast<int>(cur / k_iters);  // tile within the remainder
+        ki0 = static_cast<int>(cur - static_cast<long long>(tr) * k_iters);
         const long long left = end - cur;
         ki1 = left < k_iters - ki0 ? ki0 + static_cast<int>(left) : k_iters;
+        const int t = first_tile + tr;
         mt = t % m_tiles;
         nt = t / m_tiles;
         sp = 0;
@@ -307,6 +316,80 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             tc_fence_after();
             const int row = (mt * MT + h) * BM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            if (slab < 0 && p.splits == 1) {
+                // bf16 result, 64 columns per round.  A thread owns one row of the accumulator; the 128-byte pieces go
+                // through a per-warp shared-memory tile so that the global (or peer, over NVLink) stores are 128
+                // contiguous bytes per row and four rows per instruction instead of 16 scattered bytes.  The TMEM loads
+                // of round i+1 are issued as soon as the registers of round i are in shared memory, so their latency
+                // hides behind the stores, and the accumulator is handed back to the MMA issuer right after the
+                // last load has landed, not after the last store.
+                const uint32_t epi = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;
+                uint32_t ra[32], rb[32];
+                tmem_ld_32x32b_x32(t_row, ra);
+                tmem_ld_32x32b_x32(t_row + 32, rb);
+#pragma unroll 1
+                for (int pp = 0; pp < BN / 64; ++pp) {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int col = nt * BN + pp * 64 + half * 32;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float x0 = __uint_as_float(half ? rb[8 * v + 2 * e] : ra[8 * v + 2 * e]);
+                                float x1 = __uint_as_float(half ? rb[8 * v + 2 * e + 1] : ra[8 * v + 2 * e + 1]);
+                                if (p.per_column) {
+                                    const int pos = scale_single_pos(col + 8 * v + 2 * e);
+                                    x0 *= __half2float(p.S[pos]);
+                                    x1 *= __half2float(p.S[pos + 1]);
+                                }
+                                __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
+                                o[e] = *reinterpret_cast<uint32_t *>(&b);
+                            }
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + half * 64 + v * 16),
+                                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                         : "memory");
+                        }
+                    }
+                    if (pp + 1 < BN / 64) {
+                        tmem_ld_32x32b_x32(t_row + (pp + 1) * 64, ra);
+                        tmem_ld_32x32b_x32(t_row + (pp + 1) * 64 + 32, rb);
+                    } else {
+                        tc_fence_before();
+                        mbar_arrive(tmem_empty(acc));  // every column of this accumulator is in registers or shared memory
+                    }
+                    __syncwarp();
+                    const int piece = lane & 7;
+                    const int col_out = nt * BN + pp * 64 + piece * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = i * 4 + (lane >> 3);
+                        const int grow = (mt * MT + h) * BM + quarter * 32 + rl;
+                        uint4 val;
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                     : "r"(epi + rl * kEpiPitch + piece * 16));
+                        if (grow < p.m) {
+                            if (p.mc_c) {
+                                asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(
+                                                 p.mc_c + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out),
+                                             "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                                             : "memory");
+                            } else if (p.n_peers == 0) {
+                                *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(grow) * p.n + col_out) = val;
+                            } else {
+                                // column-parallel all-gather fused into the epilogue: plain stores into every GPU's buffer
+                                for (int pe = 0; pe < p.n_peers; ++pe)
+                                    *reinterpret_cast<uint4 *>(p.peer_c[pe] + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out) = val;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+                continue;  // the accumulator was released above
+            }
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
@@ -320,59 +403,6 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                     for (int v = 0; v < 8; ++v)
                         dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
                                              __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                } else if (p.splits == 1) {
-                    // bf16 result.  A thread owns one row x 32 columns here; the 64-byte pieces of two column chunks
-                    // go through a per-warp shared-memory tile so that the global (or peer, over NVLink) stores are
-                    // 128 contiguous bytes per row and four rows per instruction instead of 16 scattered bytes.
-                    const int col = nt * BN + cc * 32;
-                    const uint32_t epi = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float x0 = __uint_as_float(r[8 * v + 2 * e]), x1 = __uint_as_float(r[8 * v + 2 * e + 1]);
-                            if (p.per_column) {
-                                const int pos = scale_single_pos(col + 8 * v + 2 * e);
-                                x0 *= __half2float(p.S[pos]);
-                                x1 *= __half2float(p.S[pos + 1]);
-                            }
-                            __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
-                            o[e] = *reinterpret_cast<uint32_t *>(&b);
-                        }
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + (cc & 1) * 64 + v * 16),
-                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                     : "memory");
-                    }
-                    if (cc & 1) {
-                        __syncwarp();
-                        const int piece = lane & 7;
-                        const int col_out = nt * BN + (cc - 1) * 32 + piece * 8;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int rl = i * 4 + (lane >> 3);
-                            const int grow = (mt * MT + h) * BM + quarter * 32 + rl;
-                            uint4 val;
-                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
-                                         : "r"(epi + rl * kEpiPitch + piece * 16));
-                            if (grow < p.m) {
-                                if (p.mc_c) {
-                                    asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(
-                                                     p.mc_c + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out),
-                                                 "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
-                                                 : "memory");
-                                } else if (p.n_peers == 0) {
-                                    *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(grow) * p.n + col_out) = val;
-                                } else {
-                                    // column-parallel all-gather fused into the epilogue: plain stores into every GPU's buffer
-                                    for (int pe = 0; pe < p.n_peers; ++pe)
-                                        *reinterpret_cast<uint4 *>(p.peer_c[pe] + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out) = val;
-                                }
-                            }
-                        }
-                        __syncwarp();
-                    }
                 } else if (row < p.m) {
                     const int col = nt * BN + cc * 32;
                     {
@@ -541,13 +571,14 @@ __global__ void splitk_reduce_kernel(const float *partial, __nv_bfloat16 *C, con
     }
 }
 
-// Stream-K fix-up: gridDim.y blocks per output tile.  Recomputes which CTAs covered only a part of the tile's
-// K-steps (the same arithmetic as WorkIter), sums their slabs in CTA order and writes bf16.  A tile that
+// Stream-K fix-up: gridDim.y blocks per output tile of the remainder.  Recomputes which CTAs covered only a part of
+// the tile's K-steps (the same arithmetic as WorkIter), sums their slabs in CTA order and writes bf16.  A tile that
 // one CTA covered completely was already written by that CTA.
 __global__ void streamk_fixup_kernel(const float *partial, __nv_bfloat16 *C, const __half *S, int m, int n, int m_tiles,
-                                     int k_iters, int tile_rows, int bn, int ctas, long long total, int per_column) {
-    const int t = blockIdx.x;
-    const long long t0 = static_cast<long long>(t) * k_iters, t1 = t0 + k_iters;
+                                     int k_iters, int tile_rows, int bn, int ctas, long long total, int first_tile,
+                                     int per_column) {
+    const int tr = blockIdx.x;
+    const long long t0 = static_cast<long long>(tr) * k_iters, t1 = t0 + k_iters;
     int r_lo = static_cast<int>(t0 * ctas / total) - 1, r_hi = static_cast<int>(t1 * ctas / total) + 1;
     if (r_lo < 0) r_lo = 0;
     if (r_hi > ctas - 1) r_hi = ctas - 1;
@@ -560,6 +591,7 @@ __global__ void streamk_fixup_kernel(const float *partial, __nv_bfloat16 *C, con
         if (a == t0 && b == t1) return;  // whole tile by one CTA: nothing to fix up
         if (ns < 40) slabs[ns++] = 2 * r + (a == g0 ? 0 : 1);
     }
+    const int t = first_tile + tr;
     const int mt = t % m_tiles, nt = t / m_tiles;
     const size_t tile_elems = static_cast<size_t>(tile_rows) * bn;
     const int vec_per_row = bn / 4;
@@ -600,17 +632,50 @@ struct PrefillConfig {
     int bn, splits, mt, stream_k;
 };
 
-// Microseconds per 64-K step of one CTA, from measurements on B200: the dequant warps need about
-// 0.70 us for a 256-column B stage (0.37 us for 128 columns); the MMAs of one M-tile against it need
-// about 0.27 us (0.14 us).  A step costs whichever is longer.
-double step_us(int bn, int mt) {
-    const double dequant = bn == 256 ? 0.70 : 0.37, mma = (bn == 256 ? 0.27 : 0.14) * mt;
-    return dequant > mma ? dequant : mma;
+// Cost model of one launch, least-squares fitted (mean error 4 %) to 520 timed launches on B200: 5 projection shapes x
+// M = 64..8192 x 18 tilings, each timed alone after an L2 flush.  Microseconds:
+//   launch + waves * (K-steps per unit * step + tile) [+ split-K: fixed + per MB of fp32 slab traffic]
+//   stream-K: launch + whole waves as above + share * step + 2 * tile + per MB of remainder tiles + per slab piece
+// `step` is the time of one 64-K step of a CTA, `tile` what a tile adds on top (epilogue that does not overlap, pipeline
+// restart); both depend on the columns per tile and the M-tiles per stage.  On the fitted set the model's choice is
+// within 0.2 % of the best measured tiling in total.
+struct TileCost {
+    double step, tile;
+};
+TileCost tile_cost(int bn, int mt) {
+    if (mt == 2) return bn == 256 ? TileCost{0.717, 8.67} : TileCost{0.563, 1.91};
+    return bn == 256 ? TileCost{0.642, 2.74} : TileCost{0.475, 0.88};
 }
+constexpr double kCostLaunch = 11.0, kCostSplitFixed = 2.47, kCostSplitPerMB = 0.352, kCostSkPerMB = 0.693, kCostSkPerPiece = 0.0924;
+
+// Stream-K split of `tiles` tiles over `grid` CTAs: the tiles of the whole waves are dealt round-robin, the K-steps of
+// the rest go in equal shares to `ctas` CTAs.  A share is at least 8 K-steps and at least 1/36 of a tile, so that no tile
+// is spread over more slabs than the fix-up kernel sums (40).
+struct StreamKPlan {
+    int first_tile, ctas;
+};
+StreamKPlan streamk_plan(int tiles, int k_iters, int grid) {
+    StreamKPlan pl;
+    pl.first_tile = tiles / grid * grid;
+    const long long total = static_cast<long long>(tiles - pl.first_tile) * k_iters;
+    const int min_share = k_iters / 36 + 1 > 8 ? k_iters / 36 + 1 : 8;
+    long long c = total / min_share;
+    pl.ctas = static_cast<int>(c > grid ? grid : (c < 1 ? 1 : c));
+    return pl;
+}
+
+PrefillConfig g_prefill_override{0, 0, 0, 0};
 
 PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool allow_scratch = true) {
     const int sms = device_sm_count();
     const int k_iters = k / BK;
+    {  // tuning hook (kiln_w4a16_set_prefill_override): taken when it is legal for this problem, else the rule below
+        const PrefillConfig &o = g_prefill_override;
+        const bool legal = (o.bn == 128 || o.bn == 256) && n % o.bn == 0 && (o.mt == 1 || (o.mt == 2 && allow_pairs && m > BM)) &&
+                           o.splits >= 1 && o.splits <= 8 && k_iters / o.splits >= 1 && (o.stream_k == 0 || o.stream_k == 1) &&
+                           !(o.stream_k && o.splits != 1) && (allow_scratch || (o.splits == 1 && !o.stream_k));
+        if (legal) return o;
+    }
     PrefillConfig best{256, 1, 1, 0};
     double best_t = 1e30;
     const int bns[2] = {256, 128};
@@ -625,25 +690,29 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool 
                 const int m_tiles = (m + BM * mt - 1) / (BM * mt);
                 const long long units = static_cast<long long>(m_tiles) * (n / bn) * s;
                 const double waves = static_cast<double>((units + sms - 1) / sms);
-                // the epilogue of a pair is only half hidden behind the next tile
-                const double epi = mt == 2 ? (bn == 256 ? 1.5 : 0.8) : 0.3;
-                double t = waves * (static_cast<double>(k_iters) / s * step_us(bn, mt) + epi) + 1.5;
-                if (s > 1) t += 3.0 + (static_cast<double>(s) + 0.5) * m * static_cast<double>(n) * 4.0 * 2.0 / 4.0e6;
+                const TileCost tc = tile_cost(bn, mt);
+                double t = kCostLaunch + waves * (static_cast<double>(k_iters) / s * tc.step + tc.tile);
+                if (s > 1) t += kCostSplitFixed + kCostSplitPerMB * (static_cast<double>(s) + 0.5) * m * static_cast<double>(n) * 4.0 / 1.0e6;
                 if (t < best_t) {
                     best_t = t;
                     best = PrefillConfig{bn, s, mt, 0};
                 }
-                // stream-K over the same tiling: equal shares of the K-steps, plus the fix-up pass over the
-                // tiles that end up shared between CTAs (at most one per CTA)
-                if (s == 1 && allow_pairs && allow_scratch) {
+                // hybrid stream-K over the same tiling: whole waves as above, the remaining tiles' K-steps in equal
+                // shares, plus the fix-up pass over those tiles
+                if (s == 1 && allow_pairs && allow_scratch) {  // (the no-alloc entry, which passes allow_pairs = false, has no fix-up pass)
                     const long long tiles = static_cast<long long>(m_tiles) * (n / bn);
-                    const double share = static_cast<double>(tiles) * k_iters / sms;
-                    const double tile_mb = BM * mt * bn * 4.0 / 1.0e6;
-                    const double shared_tiles = tiles < sms ? static_cast<double>(tiles) : static_cast<double>(sms);
-                    const double tk = share * step_us(bn, mt) + epi * (share / k_iters + 1.0) + 1.5 + 6.0 + shared_tiles * tile_mb * 3.0 / 1.5;
-                    if (share >= 8 && tiles * k_iters >= 16LL * sms && k_iters / share + 3 <= 40 && tk < best_t) {
-                        best_t = tk;
-                        best = PrefillConfig{bn, 1, mt, 1};
+                    const StreamKPlan pl = streamk_plan(static_cast<int>(tiles), k_iters, sms);
+                    const long long rem = tiles - pl.first_tile;
+                    if (rem > 0 && rem < sms) {
+                        const double share = static_cast<double>(rem) * k_iters / pl.ctas;
+                        const double tile_mb = BM * mt * bn * 4.0 / 1.0e6;
+                        const double tk = kCostLaunch + static_cast<double>(pl.first_tile / sms) * (k_iters * tc.step + tc.tile) +
+                                          share * tc.step + 2.0 * tc.tile + kCostSkPerMB * static_cast<double>(rem) * tile_mb +
+                                          kCostSkPerPiece * static_cast<double>(rem) * k_iters / share;
+                        if (tk < best_t) {
+                            best_t = tk;
+                            best = PrefillConfig{bn, 1, mt, 1};
+                        }
                     }
                 }
             }
@@ -687,6 +756,18 @@ int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stre
 }
 
 }  // namespace
+
+void set_prefill_override(int bn, int splits, int mt, int stream_k) {
+    g_prefill_override = PrefillConfig{bn, splits, mt, stream_k};
+}
+
+void prefill_plan(int m, int n, int k, int out[4]) {
+    const PrefillConfig c = choose_prefill(m, n, k);
+    out[0] = c.bn;
+    out[1] = c.splits;
+    out[2] = c.mt;
+    out[3] = c.stream_k;
+}
 
 bool prefill_supported(int m, int n, int k, int groupsize) {
     (void)groupsize;
@@ -739,6 +820,9 @@ int launch_prefill(const GemmArgs &a) {
     for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;
     p.tile_elems = BM * c.mt * c.bn;
+    const StreamKPlan plan = streamk_plan(p.m_tiles * p.n_tiles, p.k_iters, device_sm_count());
+    p.sk_first_tile = plan.first_tile;
+    p.sk_ctas = plan.ctas;
     const size_t need = workspace_for(c, a.m, a.n);
     if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
 
@@ -757,12 +841,12 @@ int launch_prefill(const GemmArgs &a) {
         splitk_reduce_kernel<<<blocks, 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, c.splits, p.per_column);
         rc = record_cuda_error(cudaGetLastError());
     }
-    if (c.stream_k) {
-        const long long total = static_cast<long long>(p.m_tiles) * p.n_tiles * p.k_iters;
+    if (c.stream_k && p.m_tiles * p.n_tiles > plan.first_tile) {
+        const int rem = p.m_tiles * p.n_tiles - plan.first_tile;
+        const long long total = static_cast<long long>(rem) * p.k_iters;
         note_launch();
-        streamk_fixup_kernel<<<dim3(p.m_tiles * p.n_tiles, 16), 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, p.m_tiles, p.k_iters,
-                                                                         BM * c.mt, c.bn, device_sm_count(), total,
-                                                                         p.per_column);
+        streamk_fixup_kernel<<<dim3(rem, 16), 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, p.m_tiles, p.k_iters, BM * c.mt,
+                                                                  c.bn, plan.ctas, total, plan.first_tile, p.per_column);
         rc = record_cuda_error(cudaGetLastError());
     }
     return rc;

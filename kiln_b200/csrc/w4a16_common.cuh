@@ -141,6 +141,8 @@ int launch_decode(const GemmArgs &a, const DecodeOverride &ov);
 int launch_decode_regs(const GemmArgs &a, const DecodeOverride &ov);
 int launch_prefill(const GemmArgs &a);
 size_t prefill_workspace_bytes(int m, int n, int k);
+void set_prefill_override(int bn, int splits, int mt, int stream_k);
+void prefill_plan(int m, int n, int k, int out[4]);
 bool prefill_supported(int m, int n, int k, int groupsize);
 
 }  // namespace kiln

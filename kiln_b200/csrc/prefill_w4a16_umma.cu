@@ -324,6 +324,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 // hides behind the stores, and the accumulator is handed back to the MMA issuer right after the
                 // last load has landed, not after the last store.
                 const uint32_t epi = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;
+                const bool local_out = p.n_peers == 0 && !p.mc_c;
                 uint32_t ra[32], rb[32];
                 tmem_ld_32x32b_x32(t_row, ra);
                 tmem_ld_32x32b_x32(t_row + 32, rb);
@@ -348,9 +349,15 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                                 __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
                                 o[e] = *reinterpret_cast<uint32_t *>(&b);
                             }
-                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + half * 64 + v * 16),
-                                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                         : "memory");
+                            if (local_out) {
+                                if (row < p.m)
+                                    *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(row) * p.n + col + 8 * v) =
+                                        make_uint4(o[0], o[1], o[2], o[3]);
+                            } else {
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + half * 64 + v * 16),
+                                             "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                             : "memory");
+                            }
                         }
                     }
                     if (pp + 1 < BN / 64) {
@@ -360,6 +367,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                         tc_fence_before();
                         mbar_arrive(tmem_empty(acc));  // every column of this accumulator is in registers or shared memory
                     }
+                    if (local_out) continue;
                     __syncwarp();
                     const int piece = lane & 7;
                     const int col_out = nt * BN + pp * 64 + piece * 8;

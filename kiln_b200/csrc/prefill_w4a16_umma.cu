@@ -65,6 +65,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// One 2-D tile shared memory -> global through the tensor map (asynchronous; completion is tracked by the thread's bulk
+// async-group).  x (elements) must be a multiple of 8 for bf16; rows or columns past the tensor's extent are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's bulk stores have finished READING shared memory (the source may be overwritten)
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... and have been written out completely
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -191,7 +203,8 @@ struct DequantRegs {
 
 template <int BN, int MT, int DW, int DG>
 __global__ void __launch_bounds__((6 + DW + (MT == 2 ? 1 : 0)) * 32, 1)
-w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillParams p) {
+w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
+                     const PrefillParams p) {
     using C = Cfg<BN, MT, DW, DG>;
     using Regs = DequantRegs<C::kBlocksPerWarp>;
     extern __shared__ uint8_t smem_raw[];
@@ -325,6 +338,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                 // last load has landed, not after the last store.
                 const uint32_t epi = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;
                 const bool local_out = p.n_peers == 0 && !p.mc_c;
+                const uint32_t epi_tma = epi_base + static_cast<uint32_t>(warp - 2) * 4096u;  // 1024-byte aligned swizzle atoms
                 uint32_t ra[32], rb[32];
                 tmem_ld_32x32b_x32(t_row, ra);
                 tmem_ld_32x32b_x32(t_row + 32, rb);
@@ -350,9 +364,11 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                                 o[e] = *reinterpret_cast<uint32_t *>(&b);
                             }
                             if (local_out) {
-                                if (row < p.m)
-                                    *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(row) * p.n + col + 8 * v) =
-                                        make_uint4(o[0], o[1], o[2], o[3]);
+                                // 128-byte rows, 16-byte chunk index XOR (row % 8): the layout of the 128B-swizzled tensor map
+                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
+                                                 epi_tma + lane * 128 + (((half * 4 + v) ^ (lane & 7)) << 4)),
+                                             "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                             : "memory");
                             } else {
                                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + half * 64 + v * 16),
                                              "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
@@ -367,7 +383,19 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
                         tc_fence_before();
                         mbar_arrive(tmem_empty(acc));  // every column of this accumulator is in registers or shared memory
                     }
-                    if (local_out) continue;
+                    if (local_out) {
+                        // this GPU's own C: one asynchronous TMA store of the 32 x 64 tile per round (full 128-byte lines, no
+                        // load back from shared memory, nothing for this warp to wait for until it reuses the tile)
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmap_c, epi_tma, nt * BN + pp * 64, (mt * MT + h) * BM + quarter * 32);
+                            bulk_commit_group();
+                            bulk_wait_group_read0();  // (the next round's TMEM loads are already in flight)
+                        }
+                        __syncwarp();
+                        continue;
+                    }
                     __syncwarp();
                     const int piece = lane & 7;
                     const int col_out = nt * BN + pp * 64 + piece * 8;
@@ -427,6 +455,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const PrefillPa
             mbar_arrive(tmem_empty(acc));
             }
         }
+        if (lane == 0) bulk_wait_group0();  // this warp's TMA stores are complete before the CTA may exit
     } else {
         // ---------------- dequant: packed int4 -> bf16 B tile ----------------
         const int dw = (warp - kDequantWarp0) / DG, team = (warp - kDequantWarp0) % DG;  // warp `dw` of team `team`
@@ -744,8 +773,18 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Tensor map of the bf16 result [m, n] for the epilogue's TMA stores: boxes of 32 rows x 64 columns, 128-byte swizzle.
+bool encode_c_map(EncodeTiledFn enc, CUtensorMap *map, void *c, int m, int n) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * 2};
+    const cuuint32_t box[2] = {64, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, int MT = 1, int DW = 8, int DG = 2>
-int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stream) {
+int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillParams &p, cudaStream_t stream) {
     using C = Cfg<BN, MT, DW, DG>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -759,7 +798,7 @@ int launch_bn(const CUtensorMap &tmap, const PrefillParams &p, cudaStream_t stre
     const int units = p.m_tiles * p.n_tiles * p.splits;
     const int grid = p.stream_k ? device_sm_count() : (units < device_sm_count() ? units : device_sm_count());
     note_launch();
-    w4a16_prefill_kernel<BN, MT, DW, DG><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, p);
+    w4a16_prefill_kernel<BN, MT, DW, DG><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, tmap_c, p);
     return record_cuda_error(cudaGetLastError());
 }
 
@@ -806,6 +845,8 @@ int launch_prefill(const GemmArgs &a) {
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return KILN_W4A16_ERR_CUDA;
+    CUtensorMap tmap_c;  // (only used when the result goes to this GPU's own C)
+    if (!encode_c_map(enc, &tmap_c, a.C, a.m, a.n)) return KILN_W4A16_ERR_CUDA;
 
     PrefillParams p{};
     p.B = static_cast<const uint4 *>(a.B);
@@ -836,9 +877,9 @@ int launch_prefill(const GemmArgs &a) {
 
     int rc;
     if (c.mt == 2)
-        rc = c.bn == 256 ? launch_bn<256, 2>(tmap, p, a.stream) : launch_bn<128, 2>(tmap, p, a.stream);
+        rc = c.bn == 256 ? launch_bn<256, 2>(tmap, tmap_c, p, a.stream) : launch_bn<128, 2>(tmap, tmap_c, p, a.stream);
     else
-        rc = c.bn == 256 ? launch_bn<256, 1>(tmap, p, a.stream) : launch_bn<128, 1>(tmap, p, a.stream);
+        rc = c.bn == 256 ? launch_bn<256, 1>(tmap, tmap_c, p, a.stream) : launch_bn<128, 1>(tmap, tmap_c, p, a.stream);
     if (rc) return rc;
     if (c.splits > 1) {
         const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;
@@ -953,7 +994,9 @@ extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const
     p.k_iters = k / BK;
     p.per_column = groupsize == -1;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    int rc = c.bn == 256 ? launch_bn<256>(tmap, p, cs) : launch_bn<128>(tmap, p, cs);
+    CUtensorMap tmap_c;
+    if (!encode_c_map(enc, &tmap_c, C, m, n)) return KILN_W4A16_ERR_CUDA;
+    int rc = c.bn == 256 ? launch_bn<256>(tmap, tmap_c, p, cs) : launch_bn<128>(tmap, tmap_c, p, cs);
     if (rc) return rc;
     if (c.splits > 1) {
         const size_t total4 = static_cast<size_t>(m) * n / 4;

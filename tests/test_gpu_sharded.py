@@ -45,8 +45,18 @@ def _worker(rank, world, port, q):
             dense = lin.forward(a_t, row_major=True, m_chunks=chunks)
             blocked = lin.forward(a_t, m_chunks=chunks)
             torch.cuda.synchronize()
-            assert torch.equal(dense, full), "gathered columns differ from the single-GPU result"
-            assert torch.equal(blocked[rank], full[:, rank * n // world:(rank + 1) * n // world])
+            # Bit for bit, the gathered matrix is the column-wise concatenation of the per-shard GEMMs.  Against the single-GPU
+            # GEMM over all columns it may differ in the last bit: the K split (cluster size, split-K, stream-K) is chosen per
+            # problem shape, and a shard is a narrower problem, so fp32 partial sums can be added in a different order.
+            nl = n // world
+            mc = m // chunks  # the M-chunked path runs one local GEMM per chunk of rows
+            own = torch.cat([kiln_b200.matmul_bf16(a_t[c * mc:(c + 1) * mc], lin.shard) for c in range(chunks)], dim=0)
+            torch.cuda.synchronize()
+            assert torch.equal(dense[:, rank * nl:(rank + 1) * nl], own), "own columns differ from the local GEMM"
+            assert torch.equal(blocked[rank], own)
+            assert torch.equal(dense, blocked.permute(1, 0, 2).reshape(m, n)), "row-major and blocked results differ"
+            d_full = float((dense.float() - full.float()).abs().max() / full.float().abs().max())
+            assert d_full <= 2.0 ** -7, f"gathered result is {d_full} away from the single-GPU result"
             if m >= 64:  # the fused-gather epilogue lives in the tcgen05 kernel
                 sym = kiln_b200.FusedGatherOutput(m, n, dev)
                 for _ in range(2):
@@ -54,8 +64,9 @@ def _worker(rank, world, port, q):
                 torch.cuda.synchronize()
                 d = float((fused.float() - full.float()).abs().max() / full.float().abs().max())
                 assert d <= 1e-2, f"fused all-gather result differs by {d}"
-                assert torch.equal(fused[:, rank * n // world:(rank + 1) * n // world],
-                                   blocked[rank]), "own slice must equal the plain local GEMM"
+                # the fused launch never splits K (its epilogue needs whole tiles), the plain one may: same columns to 2^-7
+                d_own = float((fused[:, rank * nl:(rank + 1) * nl].float() - own.float()).abs().max() / own.float().abs().max())
+                assert d_own <= 2.0 ** -7, f"own slice of the fused result is {d_own} away from the plain local GEMM"
                 # the same through the NVSwitch multicast address, where the fabric offers one to every rank
                 has_mc = torch.tensor([1 if sym.multicast_ptr else 0], device=dev)
                 dist.all_reduce(has_mc, op=dist.ReduceOp.MIN)

@@ -147,6 +147,20 @@ kiln_w4a16_status_t kiln_w4a16_repack_device(const uint8_t *q, const uint16_t *s
                                              int groupsize, int32_t *b_packed, uint16_t *scales_perm,
                                              void *stream);
 
+/* GPTQ checkpoint tensors -> this format without dequantising.  kiln dequantises GPTQ to bf16 on the CPU at load
+ * (crates/kiln-model/src/quantized.rs:70-163) and its Marlin path then re-quantises; for symmetric checkpoints (every
+ * zero-point 8) the direct repack is exact.  qweight int32 [k/8, n] (nibble i = input row 8*row + i), qzeros int32
+ * [k/g, n/8] (nibble j = output column 8*col + j), scales fp16 bits [k/g, n] in natural column order (quantized.rs:6-14).
+ * Host: refuses with KILN_W4A16_ERR_PROB_SHAPE when a zero-point is not 8; *asymmetric (host, optional) = how many.
+ * Device: stream-ordered, cannot refuse without synchronising, so *asymmetric (DEVICE uint32, optional) receives the count
+ * and the caller discards the output if it is not 0.  No act-order (g_idx) support. */
+kiln_w4a16_status_t kiln_w4a16_repack_gptq_host(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                                                int k, int n, int groupsize, int32_t *b_packed, uint16_t *scales_perm,
+                                                uint32_t *asymmetric, int num_threads);
+kiln_w4a16_status_t kiln_w4a16_repack_gptq_device(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                                                  int k, int n, int groupsize, int32_t *b_packed, uint16_t *scales_perm,
+                                                  uint32_t *asymmetric, void *stream);
+
 /* ---- diagnostics --------------------------------------------------------------- */
 
 /* Last CUDA error code seen by this library on the calling thread (0 = none). */

@@ -45,6 +45,8 @@ SIGNATURES = {
     "kiln_w4a16_quantize_and_pack_device": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "kiln_w4a16_repack_host": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i]),
     "kiln_w4a16_repack_device": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "kiln_w4a16_repack_gptq_host": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i]),
+    "kiln_w4a16_repack_gptq_device": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "kiln_w4a16_last_cuda_error": (_i, []),
     "kiln_w4a16_check_device_status": (_i, [_vp, _vp]),
     "kiln_w4a16_set_decode_override": (None, [_i, _i, _i]),

@@ -202,6 +202,50 @@ kiln_w4a16_status_t kiln_w4a16_repack_host(const uint8_t *q, const uint16_t *sca
     return KILN_W4A16_OK;
 }
 
+
+// GPTQ checkpoint tensors -> W4A16 layout without dequantising (kiln dequantises GPTQ to bf16 on the CPU,
+// crates/kiln-model/src/quantized.rs:70-163, and the Marlin path then re-quantises that).  qweight int32 [k/8, n]
+// (nibble i of a word = input row 8*row + i), qzeros int32 [k/g, n/8] (nibble j of a word = output column 8*col + j),
+// scales fp16 [k/g, n].  GPTQ's value is (nibble - zero) * scale, this format's is (nibble - 8) * scale: the repack is
+// exact when every zero-point is 8, and refused (KILN_W4A16_ERR_PROB_SHAPE, *asymmetric = how many are not) otherwise.
+kiln_w4a16_status_t kiln_w4a16_repack_gptq_host(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                                                int k, int n, int groupsize, int32_t *b_packed, uint16_t *scales_perm,
+                                                uint32_t *asymmetric, int num_threads) {
+    if (k <= 0 || n <= 0) return KILN_W4A16_ERR_ARG;
+    if (k % 16 != 0 || n % 64 != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+    const int g = groupsize == -1 ? k : groupsize;
+    if (g <= 0 || k % g != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+    if (!qweight || !qzeros || !scales || !b_packed || !scales_perm) return KILN_W4A16_ERR_ARG;
+    const int num_groups = k / g;
+    uint32_t bad = 0;
+    for (size_t i = 0; i < static_cast<size_t>(num_groups) * (n / 8); ++i) {
+        const uint32_t z = static_cast<uint32_t>(qzeros[i]);
+        for (int j = 0; j < 8; ++j) bad += ((z >> (4 * j)) & 0xF) != static_cast<uint32_t>(kQOffset);
+    }
+    if (asymmetric) *asymmetric = bad;
+    if (bad) return KILN_W4A16_ERR_PROB_SHAPE;
+    const int chunks = n / 64;
+    const size_t row_words = static_cast<size_t>(2) * n;
+    parallel_chunks(chunks, num_threads, [&](int ch) {
+        const int c0 = ch * 64;
+        uint8_t nib[16][64];
+        for (int kb = 0; kb < k / 16; ++kb) {
+            for (int r = 0; r < 16; ++r) {
+                const int32_t *row = qweight + static_cast<size_t>((kb * 16 + r) / 8) * n + c0;
+                const int sh = 4 * ((kb * 16 + r) % 8);
+                for (int c = 0; c < 64; ++c) nib[r][c] = static_cast<uint8_t>((static_cast<uint32_t>(row[c]) >> sh) & 0xF);
+            }
+            pack_tile_host(nib, b_packed + static_cast<size_t>(kb) * row_words + ch * 128);
+        }
+        for (int grp = 0; grp < num_groups; ++grp)
+            for (int c = 0; c < 64; ++c) {
+                const int pos = groupsize == -1 ? scale_single_pos(c0 + c) : scale_group_pos(c0 + c);
+                scales_perm[static_cast<size_t>(grp) * n + pos] = scales[static_cast<size_t>(grp) * n + c0 + c];
+            }
+    });
+    return KILN_W4A16_OK;
+}
+
 }  // extern "C"
 
 // ---- device -------------------------------------------------------------------------------
@@ -277,6 +321,32 @@ __global__ void repack_words_kernel(const uint8_t *q, int n, int32_t *b_packed) 
     b_packed[static_cast<size_t>(kb) * 2 * n + ch * 128 + tid] = static_cast<int32_t>(word);
 }
 
+// GPTQ qweight int32 [k/8, n] -> packed words (same gather as above from the two GPTQ words a 16-row tile spans).
+__global__ void repack_gptq_words_kernel(const int32_t *qweight, int n, int32_t *b_packed) {
+    const int ch = blockIdx.x, kb = blockIdx.y, tid = threadIdx.x;
+    const int lane = tid >> 2, j = tid & 3;
+    const int r0 = 2 * (lane & 3), c = lane >> 2;
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = r0 + nib_dr(i), col = ch * 64 + 16 * j + c + nib_dc(i);
+        const uint32_t src = static_cast<uint32_t>(qweight[static_cast<size_t>(kb * 2 + (r >> 3)) * n + col]);
+        word |= ((src >> (4 * (r & 7))) & 0xFu) << (4 * i);
+    }
+    b_packed[static_cast<size_t>(kb) * 2 * n + ch * 128 + tid] = static_cast<int32_t>(word);
+}
+
+// counts the zero-points that are not 8 (one word = eight of them)
+__global__ void count_asymmetric_kernel(const int32_t *qzeros, size_t words, uint32_t *count) {
+    uint32_t bad = 0;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < words; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t z = static_cast<uint32_t>(qzeros[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bad += ((z >> (4 * j)) & 0xFu) != static_cast<uint32_t>(kQOffset);
+    }
+    if (bad) atomicAdd(count, bad);
+}
+
 __global__ void permute_scales_kernel(const uint16_t *scales, int n, int per_column, uint16_t *out) {
     const int col = blockIdx.x * blockDim.x + threadIdx.x, grp = blockIdx.y;
     if (col >= n) return;
@@ -326,6 +396,32 @@ kiln_w4a16_status_t kiln_w4a16_repack_device(const uint8_t *q, const uint16_t *s
     repack_words_kernel<<<dim3(n / 64, k / 16), 128, 0, st>>>(q, n, b_packed);
     permute_scales_kernel<<<dim3((n + 127) / 128, k / g), 128, 0, st>>>(scales, n, groupsize == -1, scales_perm);
     note_launch(2);
+    return record_cuda_error(cudaGetLastError());
+}
+
+// Device variant of kiln_w4a16_repack_gptq_host.  The symmetry check cannot refuse before the launch without a
+// synchronisation, so it reports: *asymmetric (a DEVICE uint32, may be NULL) receives the number of zero-points that are
+// not 8; the caller reads it (stream-ordered) and discards the output if it is not 0.
+kiln_w4a16_status_t kiln_w4a16_repack_gptq_device(const int32_t *qweight, const int32_t *qzeros, const uint16_t *scales,
+                                                  int k, int n, int groupsize, int32_t *b_packed, uint16_t *scales_perm,
+                                                  uint32_t *asymmetric, void *stream) {
+    if (k <= 0 || n <= 0) return KILN_W4A16_ERR_ARG;
+    if (k % 16 != 0 || n % 64 != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+    const int g = groupsize == -1 ? k : groupsize;
+    if (g <= 0 || k % g != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+    if (!qweight || !qzeros || !scales || !b_packed || !scales_perm) return KILN_W4A16_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned launches = 2;
+    if (asymmetric) {
+        if (int rc = record_cuda_error(cudaMemsetAsync(asymmetric, 0, sizeof(uint32_t), st))) return rc;
+        const size_t words = static_cast<size_t>(k / g) * (n / 8);
+        count_asymmetric_kernel<<<static_cast<unsigned>((words + 255) / 256 > 1024 ? 1024 : (words + 255) / 256), 256, 0, st>>>(
+            qzeros, words, asymmetric);
+        ++launches;
+    }
+    repack_gptq_words_kernel<<<dim3(n / 64, k / 16), 128, 0, st>>>(qweight, n, b_packed);
+    permute_scales_kernel<<<dim3((n + 127) / 128, k / g), 128, 0, st>>>(scales, n, groupsize == -1, scales_perm);
+    note_launch(launches);
     return record_cuda_error(cudaGetLastError());
 }
 

@@ -65,6 +65,38 @@ def pack_from_bf16(weight_t: torch.Tensor, groupsize: int = 128) -> Optional[Mar
     return MarlinPackedProj(b_packed, scales, groupsize, k, n)
 
 
+def pack_from_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor,
+                   groupsize: int = 128) -> Optional[MarlinPackedProj]:
+    """GPTQ tensors already on the GPU (qweight i32 [k/8, n], qzeros i32 [k/g, n/8], scales f16 [k/g, n]) -> packed
+    projection, on the device and without dequantising (kiln: CPU dequantise to bf16, kiln-model/src/quantized.rs:70-163,
+    then re-quantise).  Returns None when the shape is unsupported or the checkpoint is not symmetric (a zero-point other
+    than 8): the caller then keeps kiln's route.  Reads one counter back from the device."""
+    if not (qweight.is_cuda and qzeros.is_cuda and scales.is_cuda):
+        return None
+    k, n = qweight.shape[0] * 8, qweight.shape[1]
+    if not shape_is_supported(k, n) or not (groupsize == -1 or groupsize == 128):
+        return None
+    g = k if groupsize == -1 else groupsize
+    if tuple(scales.shape) != (k // g, n) or tuple(qzeros.shape) != (k // g, n // 8):
+        raise KilnMarlinError("marlin_proj: GPTQ scales / qzeros shapes do not match qweight")
+    if qweight.dtype != torch.int32 or qzeros.dtype != torch.int32:
+        raise KilnMarlinError("marlin_proj: GPTQ qweight and qzeros must be i32")
+    dev = qweight.device
+    sc = scales.to(torch.float16).contiguous()
+    b_packed = torch.empty((k // 16, 2 * n), dtype=torch.int32, device=dev)
+    s_perm = torch.empty((k // g, n), dtype=torch.float16, device=dev)
+    bad = torch.zeros(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().kiln_w4a16_repack_gptq_device(
+            qweight.contiguous().data_ptr(), qzeros.contiguous().data_ptr(), sc.data_ptr(), k, n, groupsize,
+            b_packed.data_ptr(), s_perm.data_ptr(), bad.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    if rc != 0:
+        raise KilnMarlinError(f"marlin_proj: GPTQ repack failed: {_lib.STATUS_NAMES.get(rc, rc)}")
+    if int(bad.item()) != 0:
+        return None
+    return MarlinPackedProj(b_packed, s_perm, groupsize, k, n)
+
+
 def pack_from_bf16_batch(weights: Sequence[torch.Tensor], groupsize: int = 128):
     """marlin_proj.rs:229-262: pack many projections; order preserved, None where unsupported."""
     return [pack_from_bf16(w, groupsize) for w in weights]

@@ -75,3 +75,27 @@ def repack(q, scales_f16, groupsize: int, num_threads: int = 0):
     if rc != 0:
         raise ValueError(f"kiln_w4a16_repack_host failed: {_lib.STATUS_NAMES.get(rc, rc)}")
     return packed, sp.view(np.float16)
+
+
+def repack_gptq(qweight, qzeros, scales_f16, groupsize: int, num_threads: int = 0):
+    """GPTQ checkpoint tensors (kiln-model/src/quantized.rs:6-14) -> (b_packed, scales) without dequantising.
+
+    qweight int32 [k/8, n], qzeros int32 [k/g, n/8], scales float16 [k/g, n].  Exact for symmetric checkpoints
+    (every zero-point 8); raises ValueError for any other (the caller then takes kiln's dequantise-and-requantise route).
+    """
+    qw = np.ascontiguousarray(qweight, np.int32)
+    qz = np.ascontiguousarray(qzeros, np.int32)
+    k, n = qw.shape[0] * 8, qw.shape[1]
+    s = np.ascontiguousarray(scales_f16).view(np.uint16)
+    g = k if groupsize == -1 else int(groupsize)
+    if s.shape != (k // g, n) or qz.shape != (k // g, n // 8):
+        raise ValueError(f"scales {s.shape} / qzeros {qz.shape} do not match k={k}, n={n}, groupsize={groupsize}")
+    packed = np.empty((k // 16, 2 * n), np.int32)
+    sp = np.empty_like(s)
+    bad = np.zeros(1, np.uint32)
+    rc = _lib.lib().kiln_w4a16_repack_gptq_host(_ptr(qw), _ptr(qz), _ptr(s), k, n, int(groupsize), _ptr(packed), _ptr(sp),
+                                                _ptr(bad), int(num_threads))
+    if rc != 0:
+        why = f": {int(bad[0])} zero-points are not 8 (asymmetric checkpoint)" if bad[0] else ""
+        raise ValueError(f"kiln_w4a16_repack_gptq_host failed: {_lib.STATUS_NAMES.get(rc, rc)}{why}")
+    return packed, sp.view(np.float16)

@@ -244,6 +244,33 @@ def np_gemm_fp64(a_bf16_bits: np.ndarray, q: np.ndarray, scales_f16: np.ndarray,
 # ----------------------------------------------------------------------------
 # bf16 helpers and the seeded synthetic inputs the benchmark configurations use
 # ----------------------------------------------------------------------------
+def np_gptq_pack(q: np.ndarray, zeros: np.ndarray):
+    """Builds GPTQ checkpoint tensors from nibbles q uint8 [k, n] and zero-points uint8 [k/g, n], in the layout kiln reads
+    (kiln-model/src/quantized.rs:6-14, 125-135): qweight int32 [k/8, n], nibble i of a word = input row 8*row + i;
+    qzeros int32 [k/g, n/8], nibble j of a word = output column 8*col + j."""
+    k, n = q.shape
+    qw = np.zeros((k // 8, n), np.uint32)
+    for i in range(8):
+        qw |= q[i::8].astype(np.uint32) << np.uint32(4 * i)
+    qz = np.zeros((zeros.shape[0], n // 8), np.uint32)
+    for j in range(8):
+        qz |= zeros[:, j::8].astype(np.uint32) << np.uint32(4 * j)
+    return qw.view(np.int32), qz.view(np.int32)
+
+
+def np_gptq_dequant(qweight: np.ndarray, qzeros: np.ndarray, scales_f16: np.ndarray, group_size: int) -> np.ndarray:
+    """kiln's GPTQ dequantisation (kiln-model/src/quantized.rs:118-145) as float32 [k, n] (the reference stores the
+    transpose, rounded to bf16): (nibble - zero) * scale."""
+    qw, qz = qweight.view(np.uint32), qzeros.view(np.uint32)
+    k, n = qw.shape[0] * 8, qw.shape[1]
+    rows = np.arange(k)
+    w = (qw[rows // 8] >> (4 * (rows % 8)).astype(np.uint32)[:, None]) & np.uint32(0xF)
+    cols = np.arange(n)
+    z = (qz[:, cols // 8] >> (4 * (cols % 8)).astype(np.uint32)[None, :]) & np.uint32(0xF)
+    grp = rows // group_size
+    return (w.astype(np.int32) - z[grp].astype(np.int32)).astype(np.float32) * scales_f16.astype(np.float32)[grp]
+
+
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
     u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
     lsb = (u >> 16) & 1

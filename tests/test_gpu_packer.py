@@ -69,3 +69,31 @@ def test_device_repack_prequantised_full_size_roundtrip(cuda_device):
     assert (C.unpack_fragment(pn, k, n) == q).all()
     ph, sph = kiln_b200.pack.repack(q, s, 128)
     assert (pn == ph).all() and (sp.cpu().numpy().view(np.uint16) == sph.view(np.uint16)).all()
+
+
+def test_gptq_repack_on_device(cuda_device):
+    import oracle
+
+    rng = np.random.default_rng(11)
+    k, n, g = 2560, 1024, 128
+    q = rng.integers(0, 16, (k, n), dtype=np.uint8)
+    s = (0.01 * np.abs(rng.standard_normal((k // g, n))) + 1e-3).astype(np.float16)
+    zeros = np.full((k // g, n), 8, np.uint8)
+    qw, qz = oracle.np_gptq_pack(q, zeros)
+    proj = kiln_b200.pack_from_gptq(torch.from_numpy(qw).to(cuda_device), torch.from_numpy(qz).to(cuda_device),
+                                    torch.from_numpy(s.view(np.int16).copy()).view(torch.float16).to(cuda_device), g)
+    assert proj is not None
+    assert (proj.b_packed.cpu().numpy() == oracle.C.pack_nibbles(q)).all()
+    assert (proj.scales.cpu().view(torch.int16).numpy().view(np.uint16) == oracle.C.permute_scales(s, g).view(np.uint16)).all()
+    # the packed projection multiplies like kiln's dequantised GPTQ weight
+    a = rng.standard_normal((4, k)).astype(np.float32)
+    a_t = torch.from_numpy(a).to(cuda_device).to(torch.bfloat16)
+    out = kiln_b200.matmul_bf16(a_t, proj).float().cpu().numpy()
+    w = oracle.np_gptq_dequant(qw, qz, s, g).astype(np.float64)
+    ref = a_t.float().cpu().numpy().astype(np.float64) @ w
+    assert np.abs(out - ref).max() / np.abs(ref).max() <= 1e-2
+    # asymmetric: refused (None), nothing raised
+    zeros[3, 5] = 0
+    qw2, qz2 = oracle.np_gptq_pack(q, zeros)
+    assert kiln_b200.pack_from_gptq(torch.from_numpy(qw2).to(cuda_device), torch.from_numpy(qz2).to(cuda_device),
+                                    torch.from_numpy(s.view(np.int16).copy()).view(torch.float16).to(cuda_device), g) is None

@@ -101,3 +101,34 @@ def test_concat_projections_equals_packing_the_concatenated_weight():
     assert (fused.scales.view(torch.int16).numpy().view(np.uint16) == sf.view(np.uint16)).all()
     with pytest.raises(kiln_b200.KilnMarlinError):
         kiln_b200.concat_projections(parts[:2])  # 640 columns: not a multiple of 256
+
+
+def test_gptq_repack_is_exact_for_symmetric_checkpoints_and_refused_otherwise():
+    """GPTQ tensors in kiln's layout (quantized.rs:6-14) -> the packed format: same words as packing the nibbles directly,
+    and the packed weight dequantises to exactly kiln's GPTQ dequantisation (quantized.rs:118-145)."""
+    rng = np.random.default_rng(7)
+    k, n, g = 256, 512, 128
+    q = rng.integers(0, 16, (k, n), dtype=np.uint8)
+    s = (0.01 * np.abs(rng.standard_normal((k // g, n))) + 1e-3).astype(np.float16)
+    zeros = np.full((k // g, n), 8, np.uint8)
+    qw, qz = oracle.np_gptq_pack(q, zeros)
+    packed, sp = pack.repack_gptq(qw, qz, s, g)
+    ref_p, ref_s = pack.repack(q, s, g)
+    assert (packed == ref_p).all() and (sp.view(np.uint16) == ref_s.view(np.uint16)).all()
+    assert (packed == oracle.C.pack_nibbles(q)).all()
+    # the format's value (nibble - 8) * scale against kiln's GPTQ formula (nibble - zero) * scale
+    want = oracle.np_gptq_dequant(qw, qz, s, g)
+    got = (q.astype(np.int32) - 8).astype(np.float32) * s.astype(np.float32)[np.arange(k) // g]
+    assert (want == got).all()
+    # per-column mode: one scale row, one zero row
+    s1 = s[:1]
+    qw1, qz1 = oracle.np_gptq_pack(q, zeros[:1])
+    p1, sp1 = pack.repack_gptq(qw1, qz1, s1, -1)
+    r1, rs1 = pack.repack(q, s1, -1)
+    assert (p1 == r1).all() and (sp1.view(np.uint16) == rs1.view(np.uint16)).all()
+    # an asymmetric checkpoint is refused, with the count
+    zeros[1, 37] = 7
+    zeros[0, 500] = 9
+    qw, qz = oracle.np_gptq_pack(q, zeros)
+    with pytest.raises(ValueError, match="2 zero-points"):
+        pack.repack_gptq(qw, qz, s, g)

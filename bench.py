@@ -286,6 +286,43 @@ def prefill_detail(d: Device, peaks):
     return out
 
 
+def pack_detail(d: Device):
+    """Load-time quantise + pack of one layer's MLP projections (gate, up: 2560 -> 9216; down: 9216 -> 2560) from bf16
+    weights already in HBM (device packer), and of one gate projection from host f32 (threaded host packer).  The
+    reference packs on the CPU after a device -> host copy (its own figure: 16.9 s for the 96 MLP projections of the model)."""
+    import numpy as np
+
+    t = d.torch
+    from kiln_b200 import pack as hpack
+    from kiln_b200 import pack_from_bf16
+
+    out = {}
+    total_ms = 0.0
+    for name, (k, n) in (("gate", (2560, 9216)), ("up", (2560, 9216)), ("down", (9216, 2560))):
+        w = (t.randn((k, n), device=d.dev, generator=d.gen) * 0.02).to(t.bfloat16)
+        pack_from_bf16(w)
+        t.cuda.synchronize()
+        e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            pack_from_bf16(w)
+        e1.record()
+        t.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 5
+        total_ms += ms
+        out[name] = {"device_ms": round(ms, 3), "GBps_read_plus_written": round((k * n * 2 + k * n / 2) / ms / 1e6, 1)}
+        del w
+    out["mlp_layer_device_ms"] = round(total_ms, 3)
+    out["model_96_projections_device_ms"] = round(total_ms * 32, 1)
+    wh = (np.random.default_rng(SEED).standard_normal((2560, 9216)) * 0.02).astype(np.float32)
+    hpack.quantize_and_pack(wh, 2560, 9216, 128)
+    t0 = time.perf_counter()
+    hpack.quantize_and_pack(wh, 2560, 9216, 128)
+    out["gate_host_all_threads_ms"] = round((time.perf_counter() - t0) * 1e3, 1)
+    out["reference_published"] = "16.9 s for the 96 MLP projections, CPU pack after a device->host copy (other hardware)"
+    return out
+
+
 def stack_detail(d: Device, m: int = 64):
     """Config 3: a 32-layer Qwen3.5-4B-like projection stack (24 GDN layers: GDN-in, GDN-out, gate+up, down; 8
     attention layers: q, k, v, o, gate+up, down = 144 GEMMs, distinct random int4 weights per layer, 1.6 GB, so
@@ -609,6 +646,8 @@ def run_ours(args):
         line["decode"] = decode_detail(d, peaks)
         line["prefill"] = prefill_detail(d, peaks)
         line["stack_m64"] = stack_detail(d, 64)
+        if world == 1:
+            line["pack"] = pack_detail(d)
         if world == 1:
             cases = cpu_sweep_inputs()
             cpu_sweep_once(cases)

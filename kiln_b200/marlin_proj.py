@@ -143,3 +143,59 @@ def matmul_bf16(x: torch.Tensor, proj: MarlinPackedProj) -> torch.Tensor:
         raise KilnMarlinError(f"marlin_proj: matmul_bf16 expects rank-2 or rank-3 input, got rank {x.dim()}")
     out = marlin_w4a16_gemm(x2.contiguous(), proj.b_packed, proj.scales, proj.groupsize)
     return out if lead is None else out.reshape(lead[0], lead[1], proj.n)
+
+
+class PackedCache:
+    """On-disk cache of packed projections, so that a model is quantised and packed once, not at every load
+    (kiln packs at every load: kiln-model/src/marlin_proj.rs:87-182, 16.9 s for its 96 MLP projections).
+
+    An entry is keyed by a caller-chosen name plus the shape, dtype and groupsize, and carries a checksum of the
+    source weight (the wrapping int64 sum of its 32-bit words, computed where the tensor lives), so a changed
+    checkpoint under the same name is repacked, not trusted.  Files are numpy .npz archives.
+    """
+
+    def __init__(self, directory: str):
+        import os
+
+        self.dir = directory
+        os.makedirs(directory, exist_ok=True)
+
+    @staticmethod
+    def _checksum(w: torch.Tensor) -> int:
+        flat = w.contiguous().view(torch.uint8).flatten()
+        pad = (-flat.numel()) % 4
+        if pad:
+            flat = torch.cat([flat, flat.new_zeros(pad)])
+        return int(flat.view(torch.int32).to(torch.int64).sum().item())
+
+    def _path(self, name: str, w: torch.Tensor, groupsize: int) -> str:
+        import hashlib
+        import os
+
+        tag = f"{name}|{tuple(w.shape)}|{w.dtype}|{groupsize}"
+        return os.path.join(self.dir, hashlib.sha256(tag.encode()).hexdigest()[:24] + ".npz")
+
+    def get_or_pack(self, name: str, weight_t: torch.Tensor, groupsize: int = 128) -> Optional[MarlinPackedProj]:
+        """pack_from_bf16 with the cache in front of it; the result lives on weight_t's device."""
+        import os
+
+        import numpy as np
+
+        k, n = weight_t.shape
+        if not weight_t.is_cuda or not shape_is_supported(k, n):
+            return None
+        path, chk = self._path(name, weight_t, groupsize), self._checksum(weight_t)
+        if os.path.exists(path):
+            with np.load(path) as z:
+                if int(z["checksum"]) == chk and z["b_packed"].shape == (k // 16, 2 * n):
+                    dev = weight_t.device
+                    return MarlinPackedProj(torch.from_numpy(z["b_packed"]).to(dev),
+                                            torch.from_numpy(z["scales_bits"].view(np.int16).copy()).view(torch.float16).to(dev),
+                                            groupsize, k, n)
+        proj = pack_from_bf16(weight_t, groupsize)
+        if proj is not None:
+            tmp = path + f".tmp{os.getpid()}.npz"
+            np.savez(tmp, b_packed=proj.b_packed.cpu().numpy(),
+                     scales_bits=proj.scales.cpu().view(torch.int16).numpy().view(np.uint16), checksum=np.int64(chk))
+            os.replace(tmp, path)
+        return proj

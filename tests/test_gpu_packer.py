@@ -97,3 +97,22 @@ def test_gptq_repack_on_device(cuda_device):
     qw2, qz2 = oracle.np_gptq_pack(q, zeros)
     assert kiln_b200.pack_from_gptq(torch.from_numpy(qw2).to(cuda_device), torch.from_numpy(qz2).to(cuda_device),
                                     torch.from_numpy(s.view(np.int16).copy()).view(torch.float16).to(cuda_device), g) is None
+
+
+def test_packed_cache_round_trip(cuda_device, tmp_path):
+    cache = kiln_b200.PackedCache(str(tmp_path))
+    w = (torch.randn((512, 768), device=cuda_device) * 0.02).to(torch.bfloat16)
+    first = cache.get_or_pack("layers.0.mlp.gate", w)
+    files = list(tmp_path.iterdir())
+    assert len(files) == 1
+    second = cache.get_or_pack("layers.0.mlp.gate", w)  # from disk
+    assert torch.equal(first.b_packed, second.b_packed) and torch.equal(first.scales, second.scales)
+    direct = kiln_b200.pack_from_bf16(w)
+    assert torch.equal(direct.b_packed, second.b_packed)
+    # a different weight under the same name is repacked, not served from the stale entry
+    w2 = w.clone()
+    w2[3, 5] += 0.5
+    third = cache.get_or_pack("layers.0.mlp.gate", w2)
+    assert torch.equal(third.b_packed, kiln_b200.pack_from_bf16(w2).b_packed)
+    assert len(list(tmp_path.iterdir())) == 1
+    assert cache.get_or_pack("odd", torch.zeros((100, 256), device=cuda_device, dtype=torch.bfloat16)) is None

@@ -43,6 +43,47 @@ unsafe extern "C" {
     fn kiln_w4a16_build_weight_perm(out: *mut i32);
     fn kiln_w4a16_build_scale_perm(out: *mut i32);
     fn kiln_w4a16_build_scale_perm_single(out: *mut i32);
+    // Beyond the original crate (declared for callers that want them; see include/kiln_w4a16.h):
+    /// quantise + pack on the device, straight from the bf16 / f32 `[k, n]` weight in HBM
+    pub fn kiln_w4a16_quantize_and_pack_device(
+        weight: *const c_void,
+        weight_is_bf16: i32,
+        k: i32,
+        n: i32,
+        groupsize: i32,
+        b_packed: *mut i32,
+        scales_f16: *mut u16,
+        dequant: *mut f32,
+        stream: *mut c_void,
+    ) -> i32;
+    /// GPTQ `qweight` / `qzeros` / `scales` -> this format without dequantising (symmetric checkpoints only)
+    pub fn kiln_w4a16_repack_gptq_device(
+        qweight: *const i32,
+        qzeros: *const i32,
+        scales: *const u16,
+        k: i32,
+        n: i32,
+        groupsize: i32,
+        b_packed: *mut i32,
+        scales_perm: *mut u16,
+        asymmetric: *mut u32,
+        stream: *mut c_void,
+    ) -> i32;
+    /// column-parallel GEMM whose epilogue stores into every GPU's `[m, ldc]` buffer
+    pub fn kiln_w4a16_gemm_bf16_allgather(
+        a: *const c_void,
+        b: *const c_void,
+        s: *const c_void,
+        m: i32,
+        n_local: i32,
+        k: i32,
+        groupsize: i32,
+        c_peers: *const *mut c_void,
+        n_peers: i32,
+        ldc: i32,
+        col0: i32,
+        stream: *mut c_void,
+    ) -> i32;
 }
 
 /// `a [m,k] bf16` x `b_packed [k/16, n*16/8] i32` x `scales [k/groupsize, n] f16` -> `[m,n] bf16`.

@@ -177,8 +177,8 @@ kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detai
 void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
 
 /* Tuning hook: the M at and above which the tcgen05 prefill kernel is used.  <= 0 restores the
- * built-in rule (M >= 64, or M >= 17 for weights of 16 M elements and more); a huge value
- * disables that kernel. */
+ * built-in rule (M >= 17 for weights of 16 M elements and more, M >= 33 or 49 for smaller ones, M > 256 for
+ * projections of at most 1024 columns); a huge value disables that kernel, 1 forces it. */
 void kiln_w4a16_set_prefill_min_m(int min_m);
 
 /* Tuning hook for sweeps: force the tcgen05 kernel's tiling: bn = 128 or 256 columns per tile, K splits (1..8, fp32

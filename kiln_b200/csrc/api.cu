@@ -72,17 +72,19 @@ static int validate(const GemmArgs &a) {
     return -1;  // proceed
 }
 
-// Kernel choice by M (measured on B200): the decode kernel handles 8 or 16 rows per pass and repeats the
-// int4 dequant for every pass, the tcgen05 kernel dequantises once per 128 rows.  With the default threshold
-// the tcgen05 kernel takes over at M >= 17 for large weights (>= 16 M elements: gate+up, down, GDN-in) and at
-// M >= 64 for the small ones, where its 128 x 128 tiles leave most SMs idle.  kiln_w4a16_set_prefill_min_m
-// replaces the rule by a plain threshold.
+// Kernel choice (measured on B200, CUDA-graph replay over rotating weights).  The decode kernel handles 8 or 16 rows per
+// block of CTAs and repeats the int4 dequant for every block; the tcgen05 kernel dequantises once per 128 rows but works
+// in 128-column tiles.  Crossovers: weights of 16 M elements and more (gate+up, down, GDN-in): tcgen05 from M = 17;
+// smaller ones (q, o, GDN-out): from M = 33 when N >= 4096, else from M = 49; projections of 1024 columns or fewer (k, v: four
+// to eight tiles for 148 SMs) stay on the decode kernel up to M = 256 (k at M=256: 9.4 vs 19.6 us).
+// kiln_w4a16_set_prefill_min_m replaces the rule by a plain threshold.
 static bool use_prefill(int m, int n, int k, int groupsize) {
     if (!prefill_supported(m, n, k, groupsize)) return false;
     const int min_m = g_prefill_min_m.load(std::memory_order_relaxed);
     if (min_m != kDefaultPrefillMinM) return m >= min_m;
-    if (m >= 64) return true;
-    return m >= 17 && static_cast<long long>(n) * k >= (16LL << 20);
+    if (n <= 1024) return m > 256;
+    if (static_cast<long long>(n) * k >= (16LL << 20)) return m >= 17;
+    return m >= (n >= 4096 ? 33 : 49);
 }
 
 static int gemm(const GemmArgs &a) {

@@ -16,6 +16,14 @@ from tests.util import REL_TOL, from_torch_bf16, rel_err, to_torch_bf16
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _force_tcgen05_kernel():
+    """This module tests the tcgen05 kernel: route every M to it, whatever the built-in kernel-selection rule says."""
+    _lib.lib().kiln_w4a16_set_prefill_min_m(1)
+    yield
+    _lib.lib().kiln_w4a16_set_prefill_min_m(0)
+
+
 def _case(m, k, n, seed, groupsize=128, device=None):
     a, q, s = oracle.synth_inputs(m, k, n, seed=seed, groupsize=groupsize)
     packed, sp = kiln_b200.pack.repack(q, s, groupsize)

@@ -247,6 +247,10 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_slot;
+    // Programmatic dependent launch: the next kernel in the stream may start on SMs this grid has left (or never used) and
+    // run its prologue and its weight stream there.  In this kernel only the activation loads and every global write
+    // order themselves after the previous kernel (griddepcontrol.wait); the packed weights and scales never depend on it.
+    pdl_launch_dependents();
 
     const int chunks_n = p.n >> 6;
     int mt, nt, sp, ki0, ki1, slab;
@@ -254,6 +258,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
+            pdl_wait();  // the activations may be the previous kernel's output
             uint32_t it = 0;
             bool ok = true;
             WorkIter wi(p);
@@ -317,6 +322,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     } else if (warp < kDequantWarp0) {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+        pdl_wait();  // C (or the workspace) may still be read or written by the previous kernel
         uint32_t tile = 0;
         bool ok = true;
         WorkIter wi(p);
@@ -583,6 +589,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 // out[m][n] = bf16(sum_s partial[s][m][n]) (* per-column scale)
 __global__ void splitk_reduce_kernel(const float *partial, __nv_bfloat16 *C, const __half *S, int m, int n,
                                      int splits, int per_column) {
+    pdl_launch_dependents();
+    pdl_wait();  // the partial sums come from the kernel launched just before
     const size_t total4 = static_cast<size_t>(m) * n / 4;
     const size_t slab4 = total4;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total4;
@@ -614,6 +622,8 @@ __global__ void splitk_reduce_kernel(const float *partial, __nv_bfloat16 *C, con
 __global__ void streamk_fixup_kernel(const float *partial, __nv_bfloat16 *C, const __half *S, int m, int n, int m_tiles,
                                      int k_iters, int tile_rows, int bn, int ctas, long long total, int first_tile,
                                      int per_column) {
+    pdl_launch_dependents();
+    pdl_wait();  // the slabs come from the kernel launched just before
     const int tr = blockIdx.x;
     const long long t0 = static_cast<long long>(tr) * k_iters, t1 = t0 + k_iters;
     int r_lo = static_cast<int>(t0 * ctas / total) - 1, r_hi = static_cast<int>(t1 * ctas / total) + 1;
@@ -773,6 +783,26 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+cudaLaunchAttribute pdl_attribute() {
+    cudaLaunchAttribute a = {};
+    a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    a.val.programmaticStreamSerializationAllowed = 1;
+    return a;
+}
+
+// launches a small follow-up kernel (split-K reduction, stream-K fix-up) with programmatic dependent launch
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = pdl_attribute();
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Tensor map of the bf16 result [m, n] for the epilogue's TMA stores: boxes of 32 rows x 64 columns, 128-byte swizzle.
 bool encode_c_map(EncodeTiledFn enc, CUtensorMap *map, void *c, int m, int n) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
@@ -798,8 +828,15 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillP
     const int units = p.m_tiles * p.n_tiles * p.splits;
     const int grid = p.stream_k ? device_sm_count() : (units < device_sm_count() ? units : device_sm_count());
     note_launch();
-    w4a16_prefill_kernel<BN, MT, DW, DG><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, tmap_c, p);
-    return record_cuda_error(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(C::kThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = pdl_attribute();
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG>, tmap, tmap_c, p));
 }
 
 }  // namespace
@@ -887,16 +924,16 @@ int launch_prefill(const GemmArgs &a) {
         const int cap = device_sm_count() * 8;
         if (blocks > cap) blocks = cap;
         note_launch();
-        splitk_reduce_kernel<<<blocks, 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, c.splits, p.per_column);
-        rc = record_cuda_error(cudaGetLastError());
+        rc = record_cuda_error(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), a.stream, p.partial, p.C, p.S, a.m, a.n,
+                                          c.splits, static_cast<int>(p.per_column)));
     }
     if (c.stream_k && p.m_tiles * p.n_tiles > plan.first_tile) {
         const int rem = p.m_tiles * p.n_tiles - plan.first_tile;
         const long long total = static_cast<long long>(rem) * p.k_iters;
         note_launch();
-        streamk_fixup_kernel<<<dim3(rem, 16), 256, 0, a.stream>>>(p.partial, p.C, p.S, a.m, a.n, p.m_tiles, p.k_iters, BM * c.mt,
-                                                                  c.bn, plan.ctas, total, plan.first_tile, p.per_column);
-        rc = record_cuda_error(cudaGetLastError());
+        rc = record_cuda_error(launch_pdl(streamk_fixup_kernel, dim3(rem, 16), dim3(256), a.stream, p.partial, p.C, p.S, a.m, a.n,
+                                          p.m_tiles, p.k_iters, BM * c.mt, c.bn, plan.ctas, total, plan.first_tile,
+                                          static_cast<int>(p.per_column)));
     }
     return rc;
 }
@@ -1004,8 +1041,8 @@ extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const
         const int cap = device_sm_count() * 8;
         if (blocks > cap) blocks = cap;
         note_launch();
-        splitk_reduce_kernel<<<blocks, 256, 0, cs>>>(p.partial, p.C, p.S, m, n, c.splits, p.per_column);
-        rc = record_cuda_error(cudaGetLastError());
+        rc = record_cuda_error(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), cs, p.partial, p.C, p.S, m, n, c.splits,
+                                          static_cast<int>(p.per_column)));
     }
     return rc;
 }

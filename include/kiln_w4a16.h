@@ -176,6 +176,11 @@ kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detai
  * Process-wide, not thread-safe; has no counterpart in the reference. */
 void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
 
+/* Diagnostic: the decomposition the decode kernel would use for (m, n, k) on the current device (148 SMs are
+ * assumed when no device is present), as out = {cluster_k, warps_k, warps_n, K groups staged per pass}.
+ * Follows kiln_w4a16_set_decode_override.  No counterpart in the reference. */
+void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]);
+
 /* Tuning hook: the M at and above which the tcgen05 prefill kernel is used.  <= 0 restores the
  * built-in rule (M >= 17 for weights of 16 M elements and more, M >= 33 or 49 for smaller ones, M > 256 for
  * projections of at most 1024 columns); a huge value disables that kernel, 1 forces it. */

@@ -50,6 +50,7 @@ SIGNATURES = {
     "kiln_w4a16_last_cuda_error": (_i, []),
     "kiln_w4a16_check_device_status": (_i, [_vp, _vp]),
     "kiln_w4a16_set_decode_override": (None, [_i, _i, _i]),
+    "kiln_w4a16_decode_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "kiln_w4a16_set_prefill_override": (None, [_i, _i, _i, _i]),
     "kiln_w4a16_prefill_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "kiln_w4a16_set_prefill_min_m": (None, [_i]),

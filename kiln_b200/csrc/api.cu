@@ -197,6 +197,10 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n) {
     g_decode_override = DecodeOverride{cluster_k, warps_k, warps_n};
 }
 
+void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]) {
+    if (out && m > 0 && n > 0 && k > 0) decode_plan(m, n, k, g_decode_override, out);
+}
+
 void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k) {
     set_prefill_override(bn, splits, m_tiles, stream_k);
 }

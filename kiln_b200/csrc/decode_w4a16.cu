@@ -3,49 +3,91 @@
 // Replaces the reference's `Marlin<256,1,8,8,4,8>` path
 // (kiln-marlin-gemm/csrc/marlin_kernel.cu:197-700) with a different decomposition:
 //
-//  * HBM streaming, GEMV-like.  The unit of work is one "stage": one 128-row scale group of
-//    WN adjacent 64-column chunks = 8 runs of WN*512 contiguous bytes of the packed matrix
-//    plus WN*128 bytes of scales.  A producer warp moves stages global -> shared with bulk
-//    asynchronous copies (TMA, mbarrier completion) into a ring, so the bytes in flight per SM
-//    are set by the ring depth, not by registers or by how many warps are resident, and the
-//    weight stream starts before the previous kernel in the stream has finished
-//    (programmatic dependent launch; only the activations, which the consumer warps stage
-//    themselves with plain loads, wait for it).
-//  * consumer warps: in-register int4 -> bf16 dequant (`lop3` puts each nibble pair into the
-//    mantissa of bf16x2 {128,128}); the +128+8 offset is not
-//    subtracted per weight but removed per MMA tile by one extra MMA against a constant
-//    -136 fragment; bf16 m16n8k16 tensor-core MMAs with fp32 accumulation; the fp16 group
-//    scale is applied once per 128-K group to the fp32 partial sums (exact scale).
-//  * split-K without global scratch: K is split over teams of warps inside a CTA and over
-//    the CTAs of a thread-block cluster; partial tiles meet in (distributed) shared memory
-//    and are summed in a fixed order, so results are bit-reproducible.
-//  * every wait on an mbarrier is bounded (see w4a16_async.cuh).
-#include "w4a16_async.cuh"
+//  * HBM streaming, GEMV-like.  The unit of work is one 4 KB run of the packed matrix: one 64-column chunk
+//    x one 128-row scale group = eight 512-byte rows, 16 bytes per lane each.  Every warp streams its own
+//    units straight into registers and keeps eight 16-byte loads per lane in flight: as soon as a register
+//    is consumed the load of the same row of the next unit is issued into it.  There is no producer warp,
+//    no shared-memory ring and no barrier in the stream, so the bytes in flight per SM are simply
+//    (resident warps) x 4 KB, CTAs are small (the next kernel's CTAs move in as this kernel's drain) and
+//    the first loads leave before the previous kernel in the stream has finished (programmatic dependent
+//    launch; only the activations and the output wait for it).
+//  * int4 -> fp16 in registers with five integer instructions per packed word (eight weights): `lop3` ORs
+//    the nibbles at bits 0..3 into the mantissa of 1024.0 (value 1024 + nib) and the nibbles at bits 4..7,
+//    where they sit, into the mantissa of 64.0, whose unit in the last place is 1/16 (value 64 + nib); one
+//    shift by 8 brings the other two nibble pairs into the same positions.  The activations are converted
+//    bf16 -> fp16 once when a CTA stages them (the reference kernel is fp16 on both sides,
+//    kiln-marlin-gemm/src/lib.rs:169), products are exact and accumulate in fp32.
+//  * the offsets (1024 + 8, 64 + 8) are removed per 128-K group by one extra MMA per K-tile against a constant
+//    fragment.
+//  * up to 8 rows: the MMA is issued transposed (weights are the 16x16 operand, one MMA per packed word);
+//    9..16 rows: activations are the 16x16 operand, two MMAs per packed word.
+//  * the fp16 group scale is applied once per 128-K group to the fp32 partial sums (exact scale).
+//  * split-K without global scratch: K is split over teams of warps inside a CTA and over the CTAs of a
+//    thread-block cluster; partial tiles meet in (distributed) shared memory and are summed in a fixed
+//    order, so results are bit-reproducible.
+//  * nothing in this kernel polls: the only waits are `bar.sync`, the cluster barrier (both reached by every
+//    thread on every path) and `griddepcontrol.wait`.
+#include "w4a16_common.cuh"
 
 namespace kiln {
 namespace {
 
 struct DecodeParams {
     const __nv_bfloat16 *A;
-    const uint8_t *B;  // packed weights, byte view
+    const uint4 *B;  // packed weights as 16-byte pieces: [k/16][n/64][32 lanes]
     const __half *S;
     __nv_bfloat16 *C;
-    uint32_t *status;
     int m, n, k;
     int groups;          // k / 128
     int groups_per_cta;  // K groups owned by one CTA of the cluster
+    int pass_groups;     // K groups whose activations are staged in shared memory at a time
     int warps_n, warps_k;
-    int stages;          // ring depth
-    int window;          // stages kept in flight by the producer
-    int per_column;      // groupsize == -1: one scale row, applied at the end
-    int a_pitch;         // bytes per staged activation row (groups_per_cta*256 + 16)
-    int red_pitch;       // floats per reduction row (warps_n*64 + 8)
-    // shared-memory carve-up (bytes from the 128-byte aligned base)
-    int off_ring, off_red, off_recv, off_bar, stage_bytes;
+    int per_column;  // groupsize == -1: one scale row, applied at the end
+    int a_pitch;     // bytes per staged activation row (pass_groups*256 + 16)
+    int red_pitch;   // floats per reduction row (warps_n*64 + 4 or 8)
+    int off_red, off_recv;  // shared-memory carve-up (bytes from the 128-byte aligned base)
+    int ppr_shift;          // log2 of the output pairs (two adjacent columns) per row of a CTA = 5 + log2(warps_n)
+    int own_cols;           // pairs per row owned by one rank of the cluster = ceil(pairs per row / cluster size)
+    uint32_t own_magic;     // ceil(2^32 / own_cols): x / own_cols = umulhi(x, own_magic) for the small x used here
 };
 
-__device__ __forceinline__ float half_bits_to_float(uint32_t w, int hi) {
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(hi ? (w >> 16) : (w & 0xFFFFu))));
+constexpr uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u;
+constexpr uint32_t kMagicLo = 0x64006400u;   // fp16x2 {1024, 1024}: ulp 1, a nibble at bits 0..3 adds nib
+constexpr uint32_t kMagicHi = 0x54005400u;   // fp16x2 {64, 64}: ulp 1/16, a nibble at bits 4..7 adds nib
+constexpr uint32_t kNegOffLo = 0xE408E408u;  // fp16x2 {-1032, -1032}
+constexpr uint32_t kNegOffHi = 0xD480D480u;  // fp16x2 {-72, -72}
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float half_lo(uint32_t w) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xFFFFu)));
+}
+__device__ __forceinline__ float half_hi(uint32_t w) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+}
+
+// Two bf16 (one 32-bit word) -> two fp16, round to nearest (exact inside the fp16 range).
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t x) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(x & 0xFFFF0000u)), "f"(__uint_as_float(x << 16)));
+    return r;
+}
+
+// The four fp16x2 registers of one packed word: f[0] col c, K 2qd..2qd+1; f[1] col c+8, same K;
+// f[2] col c, K 2qd+8..2qd+9; f[3] col c+8, K 2qd+8..2qd+9.  f[0], f[1] carry +1024, f[2], f[3] carry +64.
+__device__ __forceinline__ void dequant_word(uint32_t x, uint32_t (&f)[4]) {
+    const uint32_t y = x >> 8;
+    f[0] = lop3_and_or(x, kLoMask, kMagicLo);
+    f[2] = lop3_and_or(x, kHiMask, kMagicHi);
+    f[1] = lop3_and_or(y, kLoMask, kMagicLo);
+    f[3] = lop3_and_or(y, kHiMask, kMagicHi);
 }
 
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
@@ -54,285 +96,370 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
     return v;
 }
 
-// Nibble alignment shift.  Measured on B200: plain ALU shifts beat high multiplies on the FMA pipe here
-// (gate+up M=1 11.6 us vs 12.7 us; IMAD.HI issues at a quarter of the rate), so the shifts stay on the ALU.
-template <int S>
-__device__ __forceinline__ uint32_t shr_mul(uint32_t x) {
-    return x >> S;
-}
-
-// One stage for one warp: 8 K-tiles of one 64-column chunk.
-//
-// The MMA is issued transposed: the weights are its 16x16 "A" operand (16 output columns x 16 K)
-// and the activations its 16x8 "B" operand (16 K x 8 batch rows).  A packed word is exactly
-// one such A fragment -- nibble pairs (0,4) (2,6) (1,5) (3,7) are a0..a3 -- so a batch of up to 8
-// rows costs one MMA per word instead of two, and the accumulators D^T[16 cols x 8 rows] of a
-// lane sit on columns c + 8t, whose eight scales are one 16-byte run of the Marlin scale order.
 template <int NB>
-__device__ __forceinline__ void compute_stage(uint32_t w_addr, uint32_t w_kt_stride, uint32_t s_addr, bool scaled,
-                                              uint32_t a_addr, float (&acc)[4][NB][4]) {
-    float g[4][NB][4];
-    float corr[NB][4];
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) corr[nb][i] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) g[j][nb][i] = 0.f;
-    }
-    uint4 sc = make_uint4(0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u);  // fp16 ones
-    if (scaled) sc = lds_v4(s_addr);
-    const uint32_t neg[4] = {kNeg136x2, kNeg136x2, kNeg136x2, kNeg136x2};
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-        const uint4 w = lds_v4(w_addr + kt * w_kt_stride);
-        uint32_t b[NB][2];
-        if (NB == 1) {
-            asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-                         : "=r"(b[0][0]), "=r"(b[0][1])
-                         : "r"(a_addr + kt * 32));
-        } else {
-            uint32_t r[4];
-            ldmatrix_x4(r, a_addr + kt * 32);
-            b[0][0] = r[0];
-            b[0][1] = r[1];
-            b[NB - 1][0] = r[2];
-            b[NB - 1][1] = r[3];
-        }
-        const uint32_t xs[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t x = xs[j];
-            uint32_t f[4];
-            f[0] = lop3_and_or(x, kNibMask, kMagic128);              // col c,   K 2qd, 2qd+1
-            f[2] = lop3_and_or(shr_mul<4>(x), kNibMask, kMagic128);   // col c,   K 2qd+8, 2qd+9
-            f[1] = lop3_and_or(shr_mul<8>(x), kNibMask, kMagic128);   // col c+8, K 2qd, 2qd+1
-            f[3] = lop3_and_or(shr_mul<12>(x), kNibMask, kMagic128);  // col c+8, K 2qd+8, 2qd+9
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(g[j][nb], f, b[nb][0], b[nb][1]);
-        }
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) mma_bf16_16816(corr[nb], neg, b[nb][0], b[nb][1]);
-    }
+struct Acc;  // per-lane accumulators of one 64-column chunk
+
+// Up to 8 batch rows, transposed MMA: t[j][i] is column 16j + c + 8*(i/2), batch row 2qd + (i%2).
+template <>
+struct Acc<1> {
+    float t[4][4];
+};
+// 9..16 batch rows: t[n8][i] is column 8*n8 + 2qd + (i%2), batch row c + 8*(i/2).
+template <>
+struct Acc<2> {
+    float t[8][4];
+};
+
+#ifndef KILN_DECODE_JS1
+#define KILN_DECODE_JS1 2  // 16-column tiles per sweep over the K-tiles of a unit, up to 8 rows
+#endif
+#ifndef KILN_DECODE_LB1
+#define KILN_DECODE_LB1 640  // most threads of a CTA, up to 8 rows: 640 caps the kernel at 96 registers (20 warps per SM)
+#endif
+#ifndef KILN_DECODE_JS2
+#define KILN_DECODE_JS2 2  // the same for 9..16 rows
+#endif
+
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int j) { return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w)); }
+
+// One unit (8 K-tiles of one 64-column chunk) for one warp, up to 8 batch rows.  `w` holds the unit's eight
+// 16-byte pieces.  The unit is processed in sweeps over its K-tiles, JS 16-column tiles at a time (fewer
+// partial sums live at once); in the last sweep each piece is replaced by the same row of the next unit as
+// soon as it has been read.
+template <int JS>
+__device__ __forceinline__ void compute_unit_t(uint4 (&w)[8], const uint4 *next, uint32_t kt_stride, bool more,
+                                               const uint4 sc, uint32_t a_addr, Acc<1> &acc) {
+    float corr[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float s0 = half_bits_to_float(sw[j], 0), s1 = half_bits_to_float(sw[j], 1);  // cols 16j+c, 16j+c+8
+    for (int j0 = 0; j0 < 4; j0 += JS) {
+        float g[JS][4];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-            acc[j][nb][0] = fmaf(s0, g[j][nb][0] + corr[nb][0], acc[j][nb][0]);
-            acc[j][nb][1] = fmaf(s0, g[j][nb][1] + corr[nb][1], acc[j][nb][1]);
-            acc[j][nb][2] = fmaf(s1, g[j][nb][2] + corr[nb][0], acc[j][nb][2]);
-            acc[j][nb][3] = fmaf(s1, g[j][nb][3] + corr[nb][1], acc[j][nb][3]);
+        for (int j = 0; j < JS; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) g[j][i] = 0.f;
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+            const uint4 x = w[kt];
+            if (j0 + JS == 4 && more) w[kt] = ld_stream_v4(next + kt * kt_stride);
+            uint32_t b0, b1;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(a_addr + kt * 32));
+#pragma unroll
+            for (int j = 0; j < JS; ++j) {
+                uint32_t f[4];
+                dequant_word(word_of(x, j0 + j), f);
+                mma_f16_16816(g[j], f[0], f[1], f[2], f[3], b0, b1);
+            }
+            if (j0 == 0) mma_f16_16816(corr, kNegOffLo, kNegOffLo, kNegOffHi, kNegOffHi, b0, b1);
+        }
+#pragma unroll
+        for (int j = 0; j < JS; ++j) {
+            const float s0 = half_lo(sw[j0 + j]), s1 = half_hi(sw[j0 + j]);  // columns 16j + c, 16j + c + 8
+            acc.t[j0 + j][0] = fmaf(s0, g[j][0] + corr[0], acc.t[j0 + j][0]);
+            acc.t[j0 + j][1] = fmaf(s0, g[j][1] + corr[1], acc.t[j0 + j][1]);
+            acc.t[j0 + j][2] = fmaf(s1, g[j][2] + corr[0], acc.t[j0 + j][2]);
+            acc.t[j0 + j][3] = fmaf(s1, g[j][3] + corr[1], acc.t[j0 + j][3]);
         }
     }
 }
 
+// The same for 9..16 batch rows: activations are the 16x16 operand, every packed word feeds two MMAs
+// (columns 16j..16j+7 and 16j+8..16j+15).
+template <int JS>
+__device__ __forceinline__ void compute_unit_s(uint4 (&w)[8], const uint4 *next, uint32_t kt_stride, bool more,
+                                               const uint4 sc0, const uint4 sc1, uint32_t a_addr, Acc<2> &acc) {
+    // accumulator columns of this lane are 8t + 2qd + e; their scales sit at 16qd + 8e + t of the chunk's
+    // scale order: sc0 holds e = 0, sc1 holds e = 1, eight values each.
+    const uint32_t s0w[4] = {sc0.x, sc0.y, sc0.z, sc0.w}, s1w[4] = {sc1.x, sc1.y, sc1.z, sc1.w};
+    float corr[4] = {0.f, 0.f, 0.f, 0.f};  // [0], [1]: batch row c; [2], [3]: row c + 8 (every column the same)
+#pragma unroll
+    for (int j0 = 0; j0 < 4; j0 += JS) {
+        float g[2 * JS][4];
+#pragma unroll
+        for (int t = 0; t < 2 * JS; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) g[t][i] = 0.f;
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+            const uint4 x = w[kt];
+            if (j0 + JS == 4 && more) w[kt] = ld_stream_v4(next + kt * kt_stride);
+            uint32_t a[4];
+            ldmatrix_x4(a, a_addr + kt * 32);
+#pragma unroll
+            for (int j = 0; j < JS; ++j) {
+                uint32_t f[4];
+                dequant_word(word_of(x, j0 + j), f);
+                mma_f16_16816(g[2 * j], a[0], a[1], a[2], a[3], f[0], f[2]);
+                mma_f16_16816(g[2 * j + 1], a[0], a[1], a[2], a[3], f[1], f[3]);
+            }
+            if (j0 == 0) mma_f16_16816(corr, a[0], a[1], a[2], a[3], kNegOffLo, kNegOffHi);
+        }
+#pragma unroll
+        for (int tt = 0; tt < 2 * JS; ++tt) {
+            const int t = 2 * j0 + tt;
+            const float s0 = (t & 1) ? half_hi(s0w[t >> 1]) : half_lo(s0w[t >> 1]);
+            const float s1 = (t & 1) ? half_hi(s1w[t >> 1]) : half_lo(s1w[t >> 1]);
+            acc.t[t][0] = fmaf(s0, g[tt][0] + corr[0], acc.t[t][0]);
+            acc.t[t][1] = fmaf(s1, g[tt][1] + corr[0], acc.t[t][1]);
+            acc.t[t][2] = fmaf(s0, g[tt][2] + corr[2], acc.t[t][2]);
+            acc.t[t][3] = fmaf(s1, g[tt][3] + corr[2], acc.t[t][3]);
+        }
+    }
+}
+
+
+constexpr uint4 kOnesF16 = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+
 // grid = (cluster_k, n / (64*warps_n), ceil(m / (8*NB))), cluster = (cluster_k, 1, 1),
-// block = 32 * (1 + warps_n * warps_k): warp 0 produces, warp 1 + wk*warps_n + wn consumes
-// chunk wn of the stages i with i % warps_k == wk.
+// block = 32 * warps_n * warps_k: warp wk*warps_n + wn streams chunk wn of the groups i with i % warps_k == wk.
 template <int NB>
-__global__ void __launch_bounds__(288, NB == 1 ? 2 : 1) w4a16_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_decode_kernel(const DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     uint8_t *base_gen = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t sA = base, sRing = base + p.off_ring, sBar = base + p.off_bar;
-    float *sRed = reinterpret_cast<float *>(base_gen + p.off_red);
-    auto full = [&](int s) { return sBar + 8u * s; };
-    auto empty = [&](int s) { return sBar + 8u * (p.stages + s); };
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(base_gen + p.off_bar + 8 * (2 * p.stages + 1));
+    const uint32_t sA = base;
+
+    pdl_launch_dependents();
+    constexpr int kRows = 8 * NB;
+    Acc<NB> acc;
+#pragma unroll
+    for (int j = 0; j < 4 * NB; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc.t[j][i] = 0.f;
+    {  // ---- streaming part: its coordinates and pointers go out of scope before the reduction ----
+    const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
+    // A CTA may only be written through distributed shared memory once it is running: every CTA of the cluster
+    // announces itself here and checks the others just before the first remote store, long after.
+    if (csize > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int kRows = 8 * NB;
+    const int nthreads = blockDim.x;
     const int m0 = blockIdx.z * kRows;
     const int m_valid = min(kRows, p.m - m0);
-    const int chunk0 = blockIdx.y * p.warps_n;
-    const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
+    const int wn = warp % p.warps_n, wk = warp / p.warps_n;
+    const int chunk = blockIdx.y * p.warps_n + wn;
     const int gc0 = min(p.groups, static_cast<int>(rank) * p.groups_per_cta);
     const int gc1 = min(p.groups, gc0 + p.groups_per_cta);
-    const int nst = gc1 - gc0;  // stages this CTA streams
+    const int nst = gc1 - gc0;  // K groups of this CTA
+    const int qd = lane & 3, c = lane >> 2;
 
-    if (tid < p.stages) {  // one thread per ring slot (a loop in one thread cost ~0.3 us of every launch)
-        mbar_init(full(tid), 1);
-        mbar_init(empty(tid), p.warps_n);
-        if (tid == 0) *abort_flag = 0;
-        mbar_init_fence();
+    // ---- this warp's stream: local groups wk, wk + warps_k, ... of chunk `chunk` ----
+    const uint32_t chunks = static_cast<uint32_t>(p.n >> 6);
+    const uint32_t kt_stride = chunks * 32;                // 16-byte pieces between K-tiles
+    const uint32_t unit_stride = kt_stride * 8 * p.warps_k;  // ... between this warp's units
+    const uint4 *wptr = p.B + (static_cast<size_t>(gc0 + wk) * 8 * chunks + chunk) * 32 + lane;
+    // scales of a unit: NB = 1 needs the 16 bytes at position 8c of the chunk's scale order (columns c + 8t),
+    // NB = 2 the 32 bytes at 16qd (columns 8t + 2qd and 8t + 2qd + 1)
+    const uint32_t s_unit_stride = static_cast<uint32_t>(p.n) * p.warps_k / 8;
+    const uint4 *sptr = reinterpret_cast<const uint4 *>(p.S + static_cast<size_t>(gc0 + wk) * p.n + chunk * 64) +
+                        (NB == 1 ? c : 2 * qd);
+    uint4 w[8];
+    uint4 sc0 = kOnesF16, sc1 = kOnesF16;
+    int gl = wk;  // local group of the unit in flight
+    // Weights never depend on the previous kernel: the first unit is requested before waiting for it.
+    if (gl < nst) {
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) w[kt] = ld_stream_v4(wptr + kt * kt_stride);
+        if (!p.per_column) {
+            sc0 = ld_stream_v4(sptr);
+            if (NB == 2) sc1 = ld_stream_v4(sptr + 1);
+        }
     }
-    __syncthreads();
-    pdl_launch_dependents();
 
-    const int nwarps_c = p.warps_n * p.warps_k;
-    float acc[4][NB][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[j][nb][i] = 0.f;
+    // lane-constant part of the ldmatrix address.  NB = 1 (x2): lanes 0-7 address rows 0-7 at K+0, lanes 8-15 the
+    // same rows at K+8.  NB = 2 (x4): rows 0-7 / 8-15 at K+0 for lanes 0-7 / 8-15, the same at K+8 for lanes 16-31.
+    // Only the valid rows are staged: rows past m read the last valid row again (their products land in
+    // accumulator rows that are never stored).
+    uint32_t a_lane;
+    if (NB == 1) {
+        a_lane = sA + static_cast<uint32_t>(min(lane & 7, m_valid - 1)) * p.a_pitch + static_cast<uint32_t>((lane >> 3) & 1) * 16u;
+    } else {
+        a_lane = sA + static_cast<uint32_t>(min((lane & 7) + ((lane >> 3) & 1) * 8, m_valid - 1)) * p.a_pitch +
+                 static_cast<uint32_t>(lane >> 4) * 16u;
+    }
 
-    if (warp == 0) {
-        // ---------------- producer ----------------
-        const uint32_t w_row_bytes = static_cast<uint32_t>(p.warps_n) * 512u;
-        const uint32_t s_bytes = p.per_column ? 0u : static_cast<uint32_t>(p.warps_n) * 128u;
-        const uint32_t tx = 8u * w_row_bytes + s_bytes;
-        const size_t b_row_pitch = static_cast<size_t>(p.n) * 8;  // bytes per packed row (16 K)
-        bool ok = true;
-        auto issue_stage = [&](int i) {
-            const int s = i % p.stages;
-            const int g = gc0 + i;
-            const uint32_t dst = sRing + s * p.stage_bytes;
-            if (lane == 0) mbar_arrive_expect_tx(full(s), tx);
-            __syncwarp();
-            if (lane < 8)
-                bulk_g2s(dst + lane * w_row_bytes,
-                         p.B + (static_cast<size_t>(g) * 8 + lane) * b_row_pitch + static_cast<size_t>(chunk0) * 512,
-                         w_row_bytes, full(s));
-            else if (lane == 8 && s_bytes)
-                bulk_g2s(dst + 8 * w_row_bytes, p.S + static_cast<size_t>(g) * p.n + chunk0 * 64, s_bytes, full(s));
-        };
-        // Weights never depend on the previous kernel: start them before waiting for it.  Only `window`
-        // stages are kept in flight per CTA: requesting everything at once makes the memory system serve all
-        // copies side by side, so that the first stage lands about as late as the last (measured: first
-        // data after 4.2 us instead of ~1.3 us) and the consumers start late.
-        const int window = min(p.window, p.stages);
-        const int pre = min(nst, window);
-        for (int i = 0; i < pre; ++i) issue_stage(i);
-        for (int i = pre; i < nst && ok; ++i) {
-            const int j = i - window;  // this stage must have landed before stage i is requested
-            ok = mbar_wait(full(j % p.stages), (j / p.stages) & 1, abort_flag, p.status, 0x1000u | (j % p.stages));
-            if (ok && i >= p.stages) {  // slot reuse: its previous contents must have been consumed
-                const int s = i % p.stages;
-                ok = mbar_wait(empty(s), ((i / p.stages) & 1) ^ 1, abort_flag, p.status, 0x1100u | s);
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) issue_stage(i);
-        }
-        if (!ok && lane == 0) {
-            // drain what was issued before leaving (shared memory must outlive the copies)
-            for (int i = max(0, nst - p.stages); i < nst; ++i) mbar_wait_quiet(full(i % p.stages), (i / p.stages) & 1);
-        }
-    } else if (warp <= nwarps_c) {
-        // ---------------- consumers ----------------
-        const int cw = warp - 1;
-        const int wn = cw % p.warps_n, wk = cw / p.warps_n;
-        const int qd = lane & 3, c = lane >> 2;
-        // lane-constant part of the ldmatrix address.  x2: lanes 0-7 rows 0-7 at K+0, lanes 8-15 the same
-        // rows at K+8.  x4 adds rows 8-15 for lanes 16-31.
-        // Only the valid rows are staged: rows past m read the last valid row again (their products land in
-        // accumulator rows that are never stored).
-        const int a_row = min((lane & 7) + (NB == 2 ? (lane >> 4) * 8 : 0), m_valid - 1);
-        const uint32_t a_lane = sA + static_cast<uint32_t>(a_row) * p.a_pitch + static_cast<uint32_t>((lane >> 3) & 1) * 16u;
-        const uint32_t w_kt_stride = static_cast<uint32_t>(p.warps_n) * 512u;
-        bool ok = true;
-        // Activations: staged by the consumer warps themselves with plain loads (they come from L2), not by a
-        // bulk copy of the producer: a copy queued behind the weight stages in flight landed last (2.4-4.2 us
-        // after the launch) and held every consumer back.  Only this depends on the previous kernel.
-        pdl_wait();
+    // Activation staging.  The addresses of a thread's first 16-byte piece are formed here, before the wait, so that
+    // after it only load -> convert -> store -> barrier remain.
+    const int ppr_a = min(p.pass_groups, nst) * 16;  // 16-byte pieces per row in the first pass
+    const __nv_bfloat16 *a_base = p.A + static_cast<size_t>(m0) * p.k + static_cast<size_t>(gc0) * kGroup;
+    const uint4 *a_src0;
+    uint32_t a_dst0;
+    {
+        const int r0 = m_valid == 1 ? 0 : tid / max(ppr_a, 1);
+        const int c0 = tid - r0 * ppr_a;
+        a_src0 = reinterpret_cast<const uint4 *>(a_base + static_cast<size_t>(r0) * p.k + c0 * 8);
+        a_dst0 = sA + r0 * p.a_pitch + c0 * 16;
+    }
+    auto convert_store = [](uint32_t dst, const uint4 &v) {
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(bf16x2_to_f16x2(v.x)), "r"(bf16x2_to_f16x2(v.y)),
+                     "r"(bf16x2_to_f16x2(v.z)), "r"(bf16x2_to_f16x2(v.w))
+                     : "memory");
+    };
+
+    // Everything below reads A or writes C: order it after the previous kernel in the stream.
+    pdl_wait();
+
+    for (int pg0 = 0; pg0 < nst; pg0 += p.pass_groups) {
+        const int plen = min(p.pass_groups, nst - pg0);
+        if (pg0 > 0) __syncthreads();  // everyone is done with the previous pass' activations
+        // ---- stage A[m0 .. m0+m_valid, (gc0+pg0)*128 .. +plen*128) as fp16 ----
+        // A thread's first piece of the first pass goes load -> convert -> store (shortest path: its addresses were
+        // formed before the wait).  Any further pieces land raw through 16-byte asynchronous copies, all in flight at
+        // once, and are then converted in place by the thread that copied them.
         {
-            const int vec_per_row = nst * 16;  // 16-byte pieces per row in this CTA's K range
-            const int ctid = tid - 32;
-            for (int idx = ctid; idx < m_valid * vec_per_row; idx += nwarps_c * 32) {
-                const int r = idx / vec_per_row, v = idx - r * vec_per_row;
-                const uint4 val = ld_cg_v4(reinterpret_cast<const uint4 *>(
-                    p.A + static_cast<size_t>(m0 + r) * p.k + static_cast<size_t>(gc0) * kGroup + v * 8));
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sA + r * p.a_pitch + v * 16), "r"(val.x),
-                             "r"(val.y), "r"(val.z), "r"(val.w)
+            const int ppr = plen * 16;  // 16-byte pieces per row
+            const int total = m_valid * ppr;
+            const int first = pg0 == 0 ? tid + nthreads : tid;
+            const __nv_bfloat16 *a_src = a_base + static_cast<size_t>(pg0) * kGroup;
+            for (int idx = first; idx < total; idx += nthreads) {
+                const int r = idx / ppr, pc = idx - r * ppr;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sA + r * p.a_pitch + pc * 16),
+                             "l"(a_src + static_cast<size_t>(r) * p.k + pc * 8)
                              : "memory");
             }
-            asm volatile("bar.sync 1, %0;" ::"r"(nwarps_c * 32) : "memory");
+            if (pg0 == 0 && tid < total) convert_store(a_dst0, ld_cg_v4(a_src0));
+            if (first < total) {
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                for (int idx = first; idx < total; idx += nthreads) {
+                    const int r = idx / ppr, pc = idx - r * ppr;
+                    const uint32_t addr = sA + r * p.a_pitch + pc * 16;
+                    convert_store(addr, lds_v4(addr));
+                }
+            }
         }
-        for (int i = wk; i < nst && ok; i += p.warps_k) {
-            const int s = i % p.stages;
-            const uint32_t ph = (i / p.stages) & 1;
-            if (!(ok = mbar_wait(full(s), ph, abort_flag, p.status, 0x1300u | s))) break;
-            const uint32_t st = sRing + s * p.stage_bytes;
-            compute_stage<NB>(st + wn * 512u + lane * 16u, w_kt_stride, st + 8u * w_kt_stride + wn * 128u + 16u * c,
-                              !p.per_column, a_lane + static_cast<uint32_t>(i) * 256u, acc);
-            __syncwarp();
-            if (lane == 0 && nst > p.stages) mbar_arrive(empty(s));  // only a reused slot needs the release
+        __syncthreads();
+        // ---- this warp's units of the pass ----
+        for (; gl < pg0 + plen; gl += p.warps_k) {
+            const bool more = gl + p.warps_k < nst;
+            const uint4 *next = wptr + unit_stride;
+            const uint32_t a_addr = a_lane + static_cast<uint32_t>(gl - pg0) * 256u;
+            if constexpr (NB == 1)
+                compute_unit_t<KILN_DECODE_JS1>(w, next, kt_stride, more, sc0, a_addr, acc);
+            else
+                compute_unit_s<KILN_DECODE_JS2>(w, next, kt_stride, more, sc0, sc1, a_addr, acc);
+            wptr = next;
+            sptr += s_unit_stride;
+            // the next unit's scales are needed only after its eight K-tiles: request them now
+            if (more && !p.per_column) {
+                sc0 = ld_stream_v4(sptr);
+                if (NB == 2) sc1 = ld_stream_v4(sptr + 1);
+            }
         }
-        // this warp's partial tile -> shared memory: acc[j][nb][i] is column 16j + c + 8*(i/2) of the chunk,
-        // batch row 8nb + 2qd + (i%2)
-        float *mine = sRed + static_cast<size_t>(wk) * kRows * p.red_pitch;
+    }
+
+    }  // streaming part
+    // ---- this warp's partial tile -> shared memory ----
+    // Thread and block coordinates are read again here (volatile reads cannot be merged with the earlier ones), so
+    // that nothing but the accumulators has to stay in registers across the streaming loop.
+    uint32_t tid_v, by_v, bz_v;
+    asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid_v));
+    asm volatile("mov.u32 %0, %%ctaid.y;" : "=r"(by_v));
+    asm volatile("mov.u32 %0, %%ctaid.z;" : "=r"(bz_v));
+    const int tid = static_cast<int>(tid_v), lane = tid & 31, warp = tid >> 5;
+    const int qd = lane & 3, c = lane >> 2;
+    const int wn = warp % p.warps_n, wk = warp / p.warps_n;
+    const int m0 = static_cast<int>(bz_v) * kRows;
+    const int m_valid = min(kRows, p.m - m0);
+    const int nthreads = blockDim.x;
+    const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
+    float *sRed = reinterpret_cast<float *>(base_gen + p.off_red);
+    {
+        float *mine = sRed + static_cast<size_t>(wk) * kRows * p.red_pitch + wn * 64;
+        if constexpr (NB == 1) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
+            for (int j = 0; j < 4; ++j)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int row = 8 * nb + 2 * qd + (i & 1);
-                    if (row < m_valid) mine[row * p.red_pitch + wn * 64 + 16 * j + c + 8 * (i >> 1)] = acc[j][nb][i];
+                    const int row = 2 * qd + (i & 1);
+                    if (row < m_valid) mine[row * p.red_pitch + 16 * j + c + 8 * (i >> 1)] = acc.t[j][i];
                 }
+        } else {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int col = 8 * t + 2 * qd;
+                if (c < m_valid) *reinterpret_cast<float2 *>(mine + c * p.red_pitch + col) = make_float2(acc.t[t][0], acc.t[t][1]);
+                if (c + 8 < m_valid)
+                    *reinterpret_cast<float2 *>(mine + (c + 8) * p.red_pitch + col) = make_float2(acc.t[t][2], acc.t[t][3]);
+            }
+        }
     }
     __syncthreads();
 
     // ---- reduction over the K-teams of the CTA, then over the CTAs of the cluster -----------
-    // Output pairs (two adjacent columns) are dealt to the cluster ranks in contiguous slices.  Every CTA
-    // sums its K-teams and pushes each pair into the owning rank's receive buffer, slot [sender rank];
-    // after ONE cluster barrier the owner adds the slots in rank order and writes C.  Nobody touches a
-    // peer's shared memory after that barrier, so CTAs may exit without a second one.
-    const int pairs_per_row = p.warps_n * 32;
-    const int npairs = m_valid * pairs_per_row;
-    const int per_rank = (npairs + csize - 1) / csize;
-    const uint32_t recv_base = base + p.off_recv;
-    float2 *recv = reinterpret_cast<float2 *>(base_gen + p.off_recv);
-    for (int idx = tid; idx < npairs; idx += blockDim.x) {
-        const int row = idx / pairs_per_row, cp = idx - row * pairs_per_row;
-        const float *src = sRed + row * p.red_pitch + 2 * cp;
-        float2 s = *reinterpret_cast<const float2 *>(src);
-        for (int w = 1; w < p.warps_k; ++w) {
-            const float2 v = *reinterpret_cast<const float2 *>(src + static_cast<size_t>(w) * kRows * p.red_pitch);
-            s.x += v.x;
-            s.y += v.y;
-        }
-        if (csize > 1) {
-            const int owner = idx / per_rank, j = idx - owner * per_rank;
-            st_dsmem_f2(map_to_cta(recv_base + 8u * static_cast<uint32_t>(rank * per_rank + j), owner), s);
-        } else {
-            recv[idx] = s;
-        }
-    }
-    if (csize > 1)
-        cluster_sync_all();
-    else
-        __syncthreads();
-    pdl_wait();  // every thread that writes C orders itself after the previous kernel
-    const int n0 = chunk0 * 64;
-    const int i0 = min(npairs, static_cast<int>(rank) * per_rank), i1 = min(npairs, i0 + per_rank);
-    for (int idx = i0 + tid; idx < i1; idx += blockDim.x) {
-        const int row = idx / pairs_per_row, cp = idx - row * pairs_per_row;
-        float2 s = recv[idx - i0];
-        for (uint32_t r = 1; r < csize; ++r) {
-            const float2 v = recv[r * per_rank + (idx - i0)];
-            s.x += v.x;
-            s.y += v.y;
-        }
+    // An output pair is two adjacent columns of one row.  The pairs of a row are dealt to the cluster ranks in
+    // contiguous slices of `own_cols`.  Every CTA sums its K-teams and pushes each pair into the owning rank's receive
+    // buffer, slot [sender rank][row][pair]; after ONE cluster barrier the owner adds the slots in rank order and
+    // writes C.  Nobody touches a peer's shared memory after that barrier, so CTAs may exit without a second one.
+    // Everything here is a chain of dependent instructions in few threads, so it avoids divisions and keeps the
+    // shared-memory loads of a sum independent of each other.
+    const int ppr_shift = p.ppr_shift, ppr = 1 << ppr_shift;
+    const int npairs = m_valid << ppr_shift;
+    const int n0 = static_cast<int>(by_v) * (2 * ppr);
+    const size_t team_stride = static_cast<size_t>(kRows) * p.red_pitch;
+    auto store_pair = [&](int row, int cp, float2 v) {
         const int col = n0 + 2 * cp;
         if (p.per_column) {
             const int pos = scale_single_pos(col);  // col is even: col+1 sits at pos+1
-            s.x *= __half2float(p.S[pos]);
-            s.y *= __half2float(p.S[pos + 1]);
+            v.x *= __half2float(p.S[pos]);
+            v.y *= __half2float(p.S[pos + 1]);
         }
-        *reinterpret_cast<__nv_bfloat162 *>(p.C + static_cast<size_t>(m0 + row) * p.n + col) =
-            __floats2bfloat162_rn(s.x, s.y);
+        *reinterpret_cast<__nv_bfloat162 *>(p.C + static_cast<size_t>(m0 + row) * p.n + col) = __floats2bfloat162_rn(v.x, v.y);
+    };
+    const uint32_t recv_base = base + p.off_recv;
+    if (csize > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    for (int idx = tid; idx < npairs; idx += nthreads) {
+        const int row = idx >> ppr_shift, cp = idx & (ppr - 1);
+        const float *src = sRed + row * p.red_pitch + 2 * cp;
+        float2 v = *reinterpret_cast<const float2 *>(src);
+#pragma unroll 4
+        for (int t = 1; t < p.warps_k; ++t) {
+            const float2 u = *reinterpret_cast<const float2 *>(src + t * team_stride);
+            v.x += u.x;
+            v.y += u.y;
+        }
+        if (csize > 1) {
+            const uint32_t owner = __umulhi(static_cast<uint32_t>(cp), p.own_magic);
+            const uint32_t j = cp - owner * p.own_cols;
+            st_dsmem_f2(map_to_cta(recv_base + 8u * ((rank * kRows + row) * p.own_cols + j), owner), v);
+        } else {
+            store_pair(row, cp, v);
+        }
+    }
+    if (csize == 1) return;
+    cluster_sync_all();
+    {
+        const float2 *recv = reinterpret_cast<const float2 *>(base_gen + p.off_recv);
+        const int cp0 = static_cast<int>(rank) * p.own_cols;
+        const int mine = min(p.own_cols, ppr - cp0);  // pairs per row this rank owns (none for a trailing rank)
+        const int slot_stride = kRows * p.own_cols;
+        for (int idx = tid; idx < m_valid * p.own_cols; idx += nthreads) {
+            const int row = static_cast<int>(__umulhi(static_cast<uint32_t>(idx), p.own_magic));
+            const int j = idx - row * p.own_cols;
+            if (j >= mine) continue;
+            const float2 *src = recv + row * p.own_cols + j;
+            float2 v = src[0];
+#pragma unroll 4
+            for (uint32_t r = 1; r < csize; ++r) {
+                const float2 u = src[r * slot_stride];
+                v.x += u.x;
+                v.y += u.y;
+            }
+            store_pair(row, cp0 + j, v);
+        }
     }
 }
+
 
 // ---- host: decomposition heuristic and launch ---------------------------------------------
 
 struct DecodeConfig {
-    int nb, cluster_k, warps_k, warps_n, groups_per_cta, stages;
+    int nb, cluster_k, warps_k, warps_n, groups_per_cta, pass_groups;
 };
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// Shared memory one CTA may use so that two CTAs (16 consumer warps) stay resident per SM.
-constexpr int kSmemBudget = 108 * 1024;
-
-int a_stage_bytes(int rows, int groups_per_cta) { return rows * (groups_per_cta * 256 + 16); }
-int red_bytes(int nb, int wk, int wn) { return 4 * wk * 8 * nb * (wn * 64 + 8) + 8 * (8 * nb * wn * 32 + 8) + 128; }
+constexpr int kMaxWarps[3] = {0, KILN_DECODE_LB1 / 32, 16};  // per CTA, by NB (launch bounds of the kernel)
+constexpr int kStageBytes = 64 * 1024;     // activations staged per pass
 
 DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
     DecodeConfig c{};
@@ -340,78 +467,85 @@ DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
     c.nb = m <= 8 ? 1 : 2;
     const int mblocks = ceil_div(m, 8 * c.nb);
     const int sms = device_sm_count();
-    int wn = 1, ck = 1, wk = 8;
+    const int warps_sm = c.nb == 1 ? KILN_DECODE_LB1 / 32 : 16;  // resident warps per SM (register file / registers per warp)
+    int wn, ck, wk;
     if (ov.cluster_k > 0 && ov.warps_k > 0 && ov.warps_n > 0) {
         ck = ov.cluster_k;
         wk = ov.warps_k;
         wn = ov.warps_n;
     } else {
-        // Rule fitted to sweeps over (cluster_k, warps_k, warps_n) on the Qwen3.5-4B projection shapes:
-        // two chunks per CTA (1 KB bulk copies, activations shared by two warps), the smallest cluster
-        // split that gives at least one CTA per SM while every CTA keeps two or more K groups, and
-        // four K-teams (two when a batch needs two MMAs per word and the registers that go with it, or when
-        // a CTA streams eight or more groups: two long-running teams then beat four short ones).
-        wn = chunks % 2 == 0 ? 2 : 1;
-        ck = 1;
-        while (ck < 8 && static_cast<long long>(chunks / wn) * mblocks * ck < sms && groups / (ck * 2) >= 2) ck *= 2;
-        int gpc = ceil_div(groups, ck);
-        wk = (c.nb == 1 && gpc < 8) ? 4 : 2;
-        if (wk > gpc) wk = gpc;
-        // A projection so narrow that even the widest cluster split leaves most SMs idle (k, v: 512 columns):
-        // one chunk per CTA doubles the CTAs, and eight warps (whatever the number of K groups) shorten the
-        // activation staging and the reduction, which dominate such a launch.
-        if (static_cast<long long>(chunks / wn) * mblocks * 8 < sms / 2) {
-            wn = 1;
-            ck = 8;
-            while (ck > 1 && groups / ck < 2) ck /= 2;
-            wk = 8;
+        // Rule (fitted by eye to sweeps over (cluster_k, warps_k, warps_n) on B200):
+        //  * one unit per warp while all warps fit the GPU at once, else as few units per warp as that allows;
+        //  * CTAs of half an SM's warps, the K-warps of a 64-column chunk split over as many cluster ranks as that
+        //    needs, preferring a cluster size that divides the K groups;
+        //  * more than two batch rows: two chunks per CTA (four for wide projections with more than eight rows), so
+        //    that the staged activations are shared by more warps;
+        //  * a grid far smaller than the GPU is spread over more, smaller CTAs;
+        //  * the whole grid must be resident at once (one wave).
+        wn = m <= 2 ? 1 : 2;
+        if (m > 8 && chunks >= 128) wn = 4;
+        while (wn > 1 && chunks % wn) wn /= 2;
+        const long long capacity = static_cast<long long>(sms) * warps_sm;
+        int kw = groups;  // K-warps per 64-column chunk
+        const long long cols = static_cast<long long>(chunks) * mblocks;
+        if (cols * kw > capacity) {
+            const int fit = static_cast<int>(capacity / cols) > 0 ? static_cast<int>(capacity / cols) : 1;
+            kw = ceil_div(groups, ceil_div(groups, fit));
         }
-        // Measured exceptions (B200, CUDA-graph replay over rotating weights), keyed by the shape:
+        const int wk_max = (warps_sm / 2) / wn > 0 ? (warps_sm / 2) / wn : 1;
+        ck = ceil_div(kw, wk_max);
+        if (ck > 8) ck = 8;
+        for (int d = ck; d <= 8; ++d)
+            if (groups % d == 0) {
+                ck = d;
+                break;
+            }
+        if (static_cast<long long>(chunks / wn) * mblocks * ck < sms / 2) ck = groups < 8 ? groups : 8;
+        wk = ceil_div(kw, ck);
+        if (wk > wk_max) wk = wk_max;
+        const long long ctas = static_cast<long long>(chunks / wn) * mblocks * ck;
+        while (wk > 1 && ctas > static_cast<long long>(sms) * (warps_sm / (wk * wn))) --wk;
+        // Measured exceptions (B200, CUDA-graph replay over rotating weights), keyed by shape and batch class:
         struct Tuned {
-            int k, n, nb, ck, wk, wn;
+            int k, n, m_max, ck, wk, wn;
         };
         static const Tuned kTuned[] = {
-            {2560, 4096, 1, 8, 4, 1},   // q:      5.17 us at M=8 (rule: 5.44)
-            {2560, 4096, 2, 4, 4, 2},   // q:      6.31 us at M=16 (rule: 8.40)
-            {2560, 8192, 1, 4, 3, 2},   // GDN-in: 5.61 us at M=1 (rule: 6.37)
+            {2560, 4096, 2, 5, 4, 2},    {2560, 4096, 8, 4, 5, 4},   {2560, 4096, 16, 4, 5, 2},   // q
+            {2560, 512, 8, 8, 3, 1},     {2560, 512, 16, 5, 4, 1},                                // k, v
+            {4096, 2560, 2, 4, 8, 1},    {4096, 2560, 8, 8, 4, 2},   {4096, 2560, 16, 6, 6, 2},   // o, GDN-out
+            {2560, 18432, 2, 1, 10, 1},  {2560, 18432, 8, 2, 5, 2},  {2560, 18432, 16, 2, 4, 4},  // gate+up
+            {9216, 2560, 2, 6, 8, 1},    {9216, 2560, 16, 6, 6, 2},                               // down
+            {2560, 8192, 2, 1, 12, 1},   {2560, 8192, 8, 1, 20, 1},  {2560, 8192, 16, 4, 4, 4},   // GDN-in
         };
         for (const Tuned &t : kTuned)
-            if (t.k == k && t.n == n && t.nb == c.nb) {
+            if (t.k == k && t.n == n && m <= t.m_max && t.wk * t.wn <= kMaxWarps[c.nb]) {
                 ck = t.ck;
                 wk = t.wk;
                 wn = t.wn;
+                break;
             }
     }
-    while (chunks % wn) wn /= 2;
+    while (wn > 1 && chunks % wn) wn /= 2;
     if (ck > 8) ck = 8;
-    while (ck > groups) ck /= 2;
+    if (ck > groups) ck = groups;
+    if (ck < 1) ck = 1;
     c.cluster_k = ck;
-    c.warps_k = wk;
     c.warps_n = wn;
     c.groups_per_cta = ceil_div(groups, ck);
-    // Ring depth: whatever the per-CTA budget leaves.  When the CTA streams more stages than the ring
-    // holds, slots are reused, and then every slot must belong to exactly one K-team (depth a multiple
-    // of warps_k): a team that skipped a fill of a slot could not tell fills apart by barrier parity.
-    const int stage_bytes = wn * (8 * 512 + 128);
+    if (wk > c.groups_per_cta) wk = c.groups_per_cta;
+    if (wk < 1) wk = 1;
+    c.warps_k = wk;
     const int rows = m < 8 * c.nb ? m : 8 * c.nb;  // activation rows a CTA stages
-    const int room = kSmemBudget - a_stage_bytes(rows, c.groups_per_cta) - red_bytes(c.nb, wk, wn) - 512;
-    int max_stages = room / stage_bytes;
-    if (max_stages > 16) max_stages = 16;
-    if (max_stages < 1) max_stages = 1;
-    if (c.groups_per_cta <= max_stages) {
-        c.stages = c.groups_per_cta;
-    } else {
-        if (wk > max_stages) wk = max_stages;
-        c.warps_k = wk;
-        c.stages = (max_stages / wk) * wk;
-    }
+    int pg = (kStageBytes / rows - 16) / 256;
+    if (pg < 1) pg = 1;
+    c.pass_groups = c.groups_per_cta < pg ? c.groups_per_cta : pg;
     return c;
 }
 
 template <int NB>
 int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t stream) {
     static bool attr_set[64] = {};
-    constexpr int kMaxSmem = 200 * 1024;
+    constexpr int kMaxSmem = 160 * 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
@@ -420,20 +554,23 @@ int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t strea
             return rc;
         attr_set[dev] = true;
     }
-    // carve-up: [A rows][ring][reduction tiles][barriers]
+    // carve-up: [A rows][reduction tiles][receive slots]
     auto align = [](int x, int a) { return (x + a - 1) / a * a; };
-    p.a_pitch = c.groups_per_cta * 256 + 16;
-    p.stage_bytes = c.warps_n * (8 * 512 + 128);
-    p.red_pitch = c.warps_n * 64 + 8;
-    p.off_ring = align((m < 8 * NB ? m : 8 * NB) * p.a_pitch, 128);
-    p.off_red = p.off_ring + align(c.stages * p.stage_bytes, 128);
+    const int rows = m < 8 * NB ? m : 8 * NB;
+    p.a_pitch = c.pass_groups * 256 + 16;
+    p.red_pitch = c.warps_n * 64 + (NB == 1 ? 4 : 8);  // bank-conflict-free partial stores
+    p.off_red = align(rows * p.a_pitch, 128);
     p.off_recv = p.off_red + align(static_cast<int>(sizeof(float)) * c.warps_k * 8 * NB * p.red_pitch, 128);
-    p.off_bar = p.off_recv + align(8 * (8 * NB * c.warps_n * 32 + c.cluster_k), 128);
-    const size_t smem = static_cast<size_t>(p.off_bar) + 8 * (2 * c.stages + 2) + 128;
+    const int ppr = 32 * c.warps_n;  // a power of two: warps_n is 1, 2, 4 or 8
+    p.ppr_shift = 5;
+    while ((1 << p.ppr_shift) < ppr) ++p.ppr_shift;
+    p.own_cols = (ppr + c.cluster_k - 1) / c.cluster_k;
+    p.own_magic = static_cast<uint32_t>(((1ull << 32) + p.own_cols - 1) / p.own_cols);
+    const size_t smem = static_cast<size_t>(p.off_recv) + 8 * (c.cluster_k * 8 * NB * p.own_cols) + 128;
     if (smem > kMaxSmem) return KILN_W4A16_ERR_KERN_SHAPE;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(c.cluster_k, p.n / (kChunkCols * c.warps_n), (m + 8 * NB - 1) / (8 * NB));
-    cfg.blockDim = dim3(32 * (1 + c.warps_n * c.warps_k));
+    cfg.blockDim = dim3(32 * c.warps_n * c.warps_k);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
@@ -452,35 +589,30 @@ int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t strea
 
 }  // namespace
 
+void decode_plan(int m, int n, int k, const DecodeOverride &ov, int out[4]) {
+    const DecodeConfig c = choose_config(m, n, k, ov);
+    out[0] = c.cluster_k;
+    out[1] = c.warps_k;
+    out[2] = c.warps_n;
+    out[3] = c.pass_groups;
+}
+
 int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
-    if (ov.cluster_k < 0) {  // A/B hook: the register-prefetch variant
-        DecodeOverride o2{-ov.cluster_k, ov.warps_k, ov.warps_n};
-        return launch_decode_regs(a, o2);
-    }
-    uint32_t *status = device_status_word();
-    if (!status) return KILN_W4A16_ERR_CUDA;
     const DecodeConfig c = choose_config(a.m, a.n, a.k, ov);
-    if ((1 + c.warps_n * c.warps_k) * 32 > 288) return KILN_W4A16_ERR_KERN_SHAPE;
-    if (c.stages < 1 || (c.groups_per_cta > c.stages && c.stages % c.warps_k != 0)) return KILN_W4A16_ERR_KERN_SHAPE;
-    // a CTA's K range must fit the activation stage: fall back to more cluster ranks is not possible
-    // past 8, so very long K runs go through the register variant, which stages K in passes
-    if ((a.m < 8 * c.nb ? a.m : 8 * c.nb) * (c.groups_per_cta * 256 + 16) > 96 * 1024)
-        return launch_decode_regs(a, DecodeOverride{0, 0, 0});
+    if (c.warps_n * c.warps_k > kMaxWarps[c.nb] || (c.warps_n & (c.warps_n - 1))) return KILN_W4A16_ERR_KERN_SHAPE;
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16 *>(a.A);
-    p.B = static_cast<const uint8_t *>(a.B);
+    p.B = static_cast<const uint4 *>(a.B);
     p.S = static_cast<const __half *>(a.S);
     p.C = static_cast<__nv_bfloat16 *>(a.C);
-    p.status = status;
     p.m = a.m;
     p.n = a.n;
     p.k = a.k;
     p.groups = a.k / kGroup;
     p.groups_per_cta = c.groups_per_cta;
+    p.pass_groups = c.pass_groups;
     p.warps_n = c.warps_n;
     p.warps_k = c.warps_k;
-    p.stages = c.stages;
-    p.window = 8;  // swept 2..16 on B200: 8 is best by a few percent (gate+up M=1: 10.3 us vs 10.8 at 4)
     p.per_column = a.groupsize == -1;
     if (c.nb == 1) return launch_one<1>(p, c, a.m, a.stream);
     return launch_one<2>(p, c, a.m, a.stream);

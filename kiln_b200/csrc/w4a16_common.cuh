@@ -138,7 +138,7 @@ int record_cuda_error(cudaError_t e);  // returns KILN_W4A16_ERR_CUDA if e != su
 uint32_t *device_status_word();        // per-device word written by bounded waits; nullptr on failure
 
 int launch_decode(const GemmArgs &a, const DecodeOverride &ov);
-int launch_decode_regs(const GemmArgs &a, const DecodeOverride &ov);
+void decode_plan(int m, int n, int k, const DecodeOverride &ov, int out[4]);
 int launch_prefill(const GemmArgs &a);
 size_t prefill_workspace_bytes(int m, int n, int k);
 void set_prefill_override(int bn, int splits, int mt, int stream_k);

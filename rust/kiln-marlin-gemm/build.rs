@@ -23,7 +23,6 @@ fn main() {
     for f in [
         "api.cu",
         "decode_w4a16.cu",
-        "decode_w4a16_regs.cu",
         "prefill_w4a16_umma.cu",
         "repack.cu",
     ] {

@@ -89,6 +89,23 @@ def test_every_decomposition_gives_the_same_answer(cuda_device, cfg):
         lib.kiln_w4a16_set_decode_override(0, 0, 0)
 
 
+@pytest.mark.parametrize("m,k,n,cfg", [(16, 5120, 256, (1, 2, 1)), (4, 49152 + 128, 256, None), (16, 9216, 512, (1, 1, 2))])
+def test_long_k_is_staged_in_passes(cuda_device, m, k, n, cfg):
+    """A K range whose activations do not fit the shared-memory stage at once is staged in several passes
+    (the reference walks K in tiles of 64 or 128 whatever its length, marlin_kernel.cu:207-279)."""
+    lib = _lib.lib()
+    plan = (ctypes.c_int * 4)()
+    try:
+        if cfg:
+            lib.kiln_w4a16_set_decode_override(*cfg)
+        lib.kiln_w4a16_decode_plan(m, n, k, plan)
+        assert plan[3] * plan[0] < k // 128, "this case is meant to need more than one pass"
+        case = make_case(m, k, n, seed=k % 1000 + m, device=cuda_device)
+        check(case, run(case))
+    finally:
+        lib.kiln_w4a16_set_decode_override(0, 0, 0)
+
+
 def test_bit_reproducible_and_in_bounds(cuda_device):
     """Fixed reduction order: two runs agree bit for bit; canaries around the output survive."""
     case = make_case(7, 2560, 4096, seed=5, device=cuda_device)

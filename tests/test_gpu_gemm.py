@@ -89,7 +89,7 @@ def test_every_decomposition_gives_the_same_answer(cuda_device, cfg):
         lib.kiln_w4a16_set_decode_override(0, 0, 0)
 
 
-@pytest.mark.parametrize("m,k,n,cfg", [(16, 5120, 256, (1, 2, 1)), (4, 49152 + 128, 256, None), (16, 9216, 512, (1, 1, 2))])
+@pytest.mark.parametrize("m,k,n,cfg", [(16, 5120, 256, (1, 2, 1)), (8, 49152 + 128, 256, None), (16, 9216, 512, (1, 1, 2))])
 def test_long_k_is_staged_in_passes(cuda_device, m, k, n, cfg):
     """A K range whose activations do not fit the shared-memory stage at once is staged in several passes
     (the reference walks K in tiles of 64 or 128 whatever its length, marlin_kernel.cu:207-279)."""

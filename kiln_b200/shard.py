@@ -136,6 +136,7 @@ class FusedGatherOutput:
         # NVSwitch multicast address of the same buffers (0 when the fabric or the driver offers none)
         self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self._written = False  # a fused launch has stored into the group's buffers since the last reuse barrier
 
     def barrier(self):
         """Stream-ordered barrier across the group (a one-element NCCL all-reduce): when it completes on a
@@ -144,14 +145,22 @@ class FusedGatherOutput:
 
 
 def fused_column_parallel_gemm(a: torch.Tensor, lin: "ColumnParallelLinear", out: FusedGatherOutput,
-                               barrier: bool = True, multicast: Optional[bool] = None) -> torch.Tensor:
+                               barrier: bool = True, multicast: Optional[bool] = None,
+                               reuse_barrier: bool = True) -> torch.Tensor:
     """Local columns x all-gather in ONE kernel: the tcgen05 GEMM stores each finished tile into the
     [m, n] buffer of every GPU over NVLink (kiln_w4a16_gemm_bf16_allgather).  Returns this rank's full
     row-major [m, n] result.
 
     multicast=True writes each piece once to the group's NVSwitch multicast address (multimem.st,
     kiln_w4a16_gemm_bf16_allgather_multicast) instead of once per GPU; None picks it when the buffer has a
-    multicast address and the group has more than two GPUs (with two there is nothing to save)."""
+    multicast address and the group has more than two GPUs (with two there is nothing to save).
+
+    Buffer reuse: this rank's launch overwrites every OTHER rank's copy of `out`, so the readers of result i on
+    every rank must be done before any rank launches call i+1 into the same buffer.  With reuse_barrier=True
+    (default) a second stream-ordered barrier is issued before the launch whenever the buffer already holds a
+    result: a rank leaves it only after every rank's stream has reached it, i.e. after every rank's kernels that
+    read the previous result (enqueued on that stream before this call) have finished.  Pass False only when the
+    caller orders readers and writers itself, e.g. by alternating two buffers."""
     import ctypes
 
     from . import _lib
@@ -169,6 +178,9 @@ def fused_column_parallel_gemm(a: torch.Tensor, lin: "ColumnParallelLinear", out
         raise KilnMarlinError("kiln-marlin-gemm: this buffer has no multicast address")
     arr = (ctypes.c_void_p * lin.world)(*out.ptrs)
     a = a.contiguous()
+    if reuse_barrier and out._written:
+        out.barrier()
+    out._written = True
     with torch.cuda.device(a.device):
         if multicast:
             rc = _lib.lib().kiln_w4a16_gemm_bf16_allgather_multicast(

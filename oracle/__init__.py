@@ -22,20 +22,16 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
-REF_KERNEL_PATH = os.path.join(_HERE, "_ref", "libkiln_marlin_ref.so")
 
 MAX_Q = 15
 Q_OFFSET = 8
 
 
 def build(force: bool = False) -> None:
-    """Compile the C oracle (and the reference CUDA TU when its sources are present)."""
+    """Compile the C oracle."""
     src = os.path.join(_HERE, "w4a16_oracle.c")
     if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
-    ref_src = "/root/reference/crates/kiln-marlin-gemm/csrc/marlin_kernel.cu"
-    if os.path.exists(ref_src) and (force or not os.path.exists(REF_KERNEL_PATH)):
-        subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
 
 
 _lib = None
@@ -69,6 +65,11 @@ def _c(a, dtype):
 # ctypes face of w4a16_oracle.c
 # ----------------------------------------------------------------------------
 class C:
+    @staticmethod
+    def set_num_threads(n: int) -> None:
+        """Threads the OpenMP loops of the C oracle use from now on (a launcher may have exported OMP_NUM_THREADS=1)."""
+        _load().oracle_set_num_threads(int(n))
+
     @staticmethod
     def num_threads() -> int:
         return int(_load().oracle_num_threads())

@@ -8,20 +8,22 @@
  * there only as the checker / the timed CPU baseline.
  *
  * What pins this oracle:
- *   - The packed-weight and permuted-scale FORMAT (steps a2/a3) is pinned on a
- *     GPU by feeding this oracle's packed output to the reference's own CUDA
- *     kernel (compiled unmodified into oracle/_ref) and checking that kernel's
- *     output against `oracle_gemm_fp64` (tests/test_gpu_reference_kernel.py),
- *     and on the CPU by an independent fragment-formula unpacker
- *     (`oracle_unpack_fragment`) derived from the mma.m16n8k16 register layout
- *     the reference kernel feeds (csrc/marlin_kernel.cu:131-152, 442-461).
+ *   - The packed-weight and permuted-scale FORMAT (steps a2/a3) is PARITY UNPINNED in the strict sense: the
+ *     reference holds no golden vector, known-answer test or fixture for the packed bytes, its Rust packer cannot be
+ *     built here (no cargo/rustc), and its CUDA kernel, compiled unmodified for sm_100a, ended its first launch on a
+ *     B200 with "an illegal instruction was encountered" and is not run again.  What holds the format in place is
+ *     weaker: this restatement keeps the loop order and temporaries of crates/kiln-marlin-gemm/src/lib.rs:296-357,
+ *     429-528; an independent vectorised numpy restatement (oracle/__init__.py) agrees with it bit for bit; and an
+ *     unpacker written from the consumer side (`oracle_unpack_fragment`, the mma.m16n8k16 register ownership the
+ *     reference kernel feeds, csrc/marlin_kernel.cu:131-152, 442-461) inverts it on every tested shape.
  *   - The QUANTISER (step a1) is pinned against the reference's own numpy
  *     restatement (scripts/c11_marlin_audit.py:208-241) on tie-free inputs;
  *     the tie rule itself (round half away from zero, Rust `f32::round`) has
  *     no golden vector anywhere in the reference: that detail is "parity
  *     unpinned" and follows crates/kiln-marlin-gemm/src/lib.rs:422 by reading.
- *   - The reference ships no golden vectors or fixtures for this path; the
- *     Rust packer cannot be built here (no cargo/rustc).
+ *   - The GPTQ layout restated in oracle/__init__.py (`np_gptq_pack`, `np_gptq_dequant`) is pinned to the two
+ *     known-answer tests the reference holds for it (crates/kiln-model/src/quantized.rs:311-415), reproduced in
+ *     tests/test_oracle_golden.py.
  */
 #include <math.h>
 #include <stdint.h>
@@ -368,6 +370,10 @@ int oracle_w4a16_gemm_cpu(const uint16_t *a, const uint8_t *q, const uint16_t *s
 #ifdef _OPENMP
 #include <omp.h>
 int oracle_num_threads(void) { return omp_get_max_threads(); }
+void oracle_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
 #else
 int oracle_num_threads(void) { return 1; }
+void oracle_set_num_threads(int n) { (void)n; }
 #endif

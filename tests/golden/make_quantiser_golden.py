@@ -2,7 +2,7 @@
 the quantiser (kiln: scripts/c11_marlin_audit.py:208-241, `marlin_dequant_groupwise`).
 
 Run in a container that has the kiln tree mounted:
-    python tests/golden/make_quantiser_golden.py /root/reference
+    python tests/golden/make_quantiser_golden.py <path of the kiln tree>     (or KILN_REF in the environment)
 The fixture holds the seed-derived input and that function's outputs; the test suite never
 needs the kiln tree.
 """
@@ -31,4 +31,4 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["KILN_REF"])

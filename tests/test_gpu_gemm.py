@@ -7,7 +7,9 @@ import pytest
 import torch
 
 import kiln_b200
+import oracle
 from kiln_b200 import _lib
+from oracle import C
 from tests.util import QWEN_SHAPES, REL_TOL, from_torch_bf16, make_case, rel_err, to_torch_bf16
 
 pytestmark = pytest.mark.gpu
@@ -52,6 +54,27 @@ def test_reference_parity_shapes(cuda_device, m, k, n):
     torch.cuda.synchronize()
     assert out.shape == (m, n) and out.dtype == torch.bfloat16
     assert rel_err(from_torch_bf16(out), ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("name", ["q", "k", "o", "gate_up", "down", "gdn_in"])
+def test_stack_shapes_at_m64(cuda_device, name):
+    """Continuous-batch M=64 on the six distinct projection shapes of the 32-layer stack configuration, with whatever
+    kernel the built-in rule picks.  fp64 oracle on sampled rows, float32 torch matmul on the whole output."""
+    k, n = QWEN_SHAPES[name]
+    m = 64
+    a, q, s = oracle.synth_inputs(m, k, n, seed=640 + len(name))
+    packed, sp = kiln_b200.pack.repack(q, s, 128)
+    a_t = to_torch_bf16(a, cuda_device)
+    out = kiln_b200.marlin_w4a16_gemm(a_t, torch.from_numpy(packed).to(cuda_device),
+                                      torch.from_numpy(sp.view(np.int16).copy()).view(torch.float16).to(cuda_device), 128)
+    torch.cuda.synchronize()
+    sel = np.array([0, 7, 8, 15, 16, 31, 47, 63])
+    ref = C.gemm_fp64(a[sel], q, s, 128)
+    assert rel_err(from_torch_bf16(out[torch.from_numpy(sel).to(cuda_device)]), ref) <= REL_TOL
+    w = (torch.from_numpy(q.astype(np.float32)).to(cuda_device) - 8.0) * \
+        torch.from_numpy(s.astype(np.float32)).to(cuda_device).repeat_interleave(128, dim=0)
+    full = a_t.float() @ w
+    assert float((out.float() - full).abs().max() / full.abs().max()) <= REL_TOL
 
 
 @pytest.mark.parametrize("m", [2, 3, 5, 7, 9, 15, 17, 31, 32, 33, 63, 64, 65, 100])

@@ -3,6 +3,8 @@
 The fp64 oracle is evaluated on a sample of rows (every output row depends on one row of A only), and the
 whole output is also compared with a float32 torch matmul of the dequantised weight on the GPU.
 Tolerance: max|out - ref| / max|ref| <= 1e-2."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -76,6 +78,28 @@ def test_prefill_benchmark_shapes(cuda_device):
         case = _case(m, k, n, seed=7, device=cuda_device)
         out = kiln_b200.marlin_w4a16_gemm(case["a_t"], case["b_t"], case["s_t"], 128)
         _check(case, out, rows=8)
+
+
+@pytest.mark.parametrize("name,k,n", [("gate_up", 2560, 18432), ("down", 9216, 2560)])
+def test_prefill_m8192_with_the_rules_own_tiling(cuda_device, name, k, n):
+    """Chunked-prefill configuration at its largest M, nothing forced: on the down projection the built-in rule picks
+    hybrid stream-K here (320 tiles on 148 SMs), on gate+up pairs of M-tiles."""
+    m = 8192
+    plan = (ctypes.c_int * 4)()
+    _lib.lib().kiln_w4a16_prefill_plan(m, n, k, plan)
+    if name == "down":
+        assert plan[3] == 1 or plan[1] > 1, f"expected a K-splitting plan for {name}, got {list(plan)}"
+    case = _case(m, k, n, seed=8192 + n, device=cuda_device)
+    out = kiln_b200.marlin_w4a16_gemm(case["a_t"], case["b_t"], case["s_t"], 128)
+    _check(case, out, rows=6)
+
+
+def test_shard_shape_of_the_column_parallel_configuration(cuda_device):
+    """M=16384, K=9216, N=9216: what one of eight GPUs computes in the N-sharded configuration (N=73728)."""
+    m, k, n = 16384, 9216, 9216
+    case = _case(m, k, n, seed=4, device=cuda_device)
+    out = kiln_b200.marlin_w4a16_gemm(case["a_t"], case["b_t"], case["s_t"], 128)
+    _check(case, out, rows=4)
 
 
 def test_prefill_per_column(cuda_device):

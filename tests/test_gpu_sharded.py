@@ -31,7 +31,12 @@ def _worker(rank, world, port, q):
 
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+
+    # a short timeout: if one rank fails an assertion and leaves, its peer's next collective ends with an error
+    # instead of spinning on the GPU
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
+    ok = False
     try:
         for m, k, n, chunks in [(4, 512, 1024, 1), (256, 640, 1024, 1), (256, 640, 1024, 2)]:
             a, qn, s = oracle.synth_inputs(m, k, n, seed=40 + m)
@@ -59,9 +64,13 @@ def _worker(rank, world, port, q):
             assert d_full <= 2.0 ** -7, f"gathered result is {d_full} away from the single-GPU result"
             if m >= 64:  # the fused-gather epilogue lives in the tcgen05 kernel
                 sym = kiln_b200.FusedGatherOutput(m, n, dev)
-                for _ in range(2):
-                    fused = kiln_b200.fused_column_parallel_gemm(a_t, lin, sym)
+                # two calls into the same buffer with different activations: the second may only overwrite a peer's copy
+                # after that peer has read the first result (the clone below is enqueued before the second call)
+                a_neg = (-a_t).contiguous()
+                first = kiln_b200.fused_column_parallel_gemm(a_neg, lin, sym).clone()
+                fused = kiln_b200.fused_column_parallel_gemm(a_t, lin, sym)
                 torch.cuda.synchronize()
+                assert torch.equal(first, -fused), "the first result was overwritten before it was read"
                 d = float((fused.float() - full.float()).abs().max() / full.float().abs().max())
                 assert d <= 1e-2, f"fused all-gather result differs by {d}"
                 # the fused launch never splits K (its epilogue needs whole tiles), the plain one may: same columns to 2^-7
@@ -81,12 +90,16 @@ def _worker(rank, world, port, q):
             ref = C.gemm_fp64(a, qn, s, 128)
             got = oracle.bf16_bits_to_f32(dense.cpu().view(torch.int16).numpy().view(np.uint16))
             assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+        ok = True
         q.put((rank, "ok"))
     except Exception as e:  # pragma: no cover
         q.put((rank, repr(e)))
     finally:
-        dist.barrier()
-        dist.destroy_process_group()
+        # no collective on the failure path: a rank that failed leaves between steps with nothing of its own in flight
+        torch.cuda.synchronize()
+        if ok:
+            dist.barrier()
+            dist.destroy_process_group()
 
 
 def test_two_gpu_column_parallel():
@@ -98,7 +111,16 @@ def test_two_gpu_column_parallel():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in procs]
+    res = []
+    try:
+        for _ in procs:
+            res.append(q.get(timeout=300))
+    except Exception as e:  # queue.Empty: a rank never reported
+        res.append(("parent", repr(e)))
     for p in procs:
-        p.join(60)
-    assert sorted(res) == [(0, "ok"), (1, "ok")], res
+        p.join(90)
+    for p in procs:  # a child that outlived both waits is stopped by its exact handle
+        if p.is_alive():
+            p.terminate()
+            p.join(10)
+    assert sorted(res, key=str) == [(0, "ok"), (1, "ok")], res

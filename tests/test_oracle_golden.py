@@ -108,3 +108,38 @@ def test_kiln_lcg_restated():
         exp.append(np.float32(np.float32((state >> 33) & 0x7FFFFFFF) / np.float32(2147483647)) - np.float32(0.5))
     assert v.tolist() == [float(e) for e in exp]
     assert np.abs(v).max() <= 0.5
+
+
+def test_gptq_layout_matches_the_references_known_answers():
+    """The oracle's restatement of kiln's GPTQ layout (quantized.rs:118-145) reproduces the two known-answer tests
+    the reference holds for it (quantized.rs:311-372: all nibbles 5, zero-point 8, scale 0.5 -> -1.5 everywhere;
+    :374-415: nibbles 0..7 in one word, zero-point 0, scale 1 -> 0..7 by input row, which fixes the nibble order),
+    and `np_gptq_pack` is its inverse on both."""
+    import json
+    import os
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "gptq_known_answers.json")) as f:
+        cases = json.load(f)["cases"]
+    for c in cases:
+        k, n, g = c["in_features"], c["out_features"], c["group_size"]
+        qw = np.array(c["qweight_words_u32"], np.uint32).reshape(c["qweight_shape"]).view(np.int32)
+        qz = np.array(c["qzeros_words_u32"], np.uint32).reshape(c["qzeros_shape"]).view(np.int32)
+        sc = np.array(c["scales"], np.float16).reshape(c["scales_shape"])
+        npad = qz.shape[1] * 8  # the zero-point words cover eight output columns each
+        qw_p = np.zeros((k // 8, npad), np.int32)
+        qw_p[:, :n] = qw
+        sc_p = np.zeros((k // g, npad), np.float16)
+        sc_p[:, :n] = sc
+        w = oracle.np_gptq_dequant(qw_p, qz, sc_p, g)[:, :n]
+        assert w.shape == (k, n)
+        if "expected_every_element" in c:
+            assert (w == c["expected_every_element"]).all()
+        else:
+            assert (w[:, 0] == np.array(c["expected_by_input_row"], np.float32)).all()
+        # the packer of the same layout is the inverse: nibbles and zero-points in, the same words out
+        rows = np.arange(k)
+        nib = ((qw_p.view(np.uint32)[rows // 8] >> (4 * (rows % 8)).astype(np.uint32)[:, None]) & 0xF).astype(np.uint8)
+        cols = np.arange(npad)
+        zer = ((qz.view(np.uint32)[:, cols // 8] >> (4 * (cols % 8)).astype(np.uint32)[None, :]) & 0xF).astype(np.uint8)
+        qw2, qz2 = oracle.np_gptq_pack(nib, zer)
+        assert (qw2 == qw_p).all() and (qz2 == qz).all()

@@ -255,6 +255,46 @@ def decode_detail(d: Device, peaks):
             gbs = alg_bytes(m, k, n) / us / 1e3
             out[f"{name}:m{m}"] = {"us": round(us, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4)}
         del ws
+    out.update(fused_rows_detail(d, peaks))
+    return out
+
+
+def fused_rows_detail(d: Device, peaks):
+    """Sibling projections as the library recommends issuing them: q, k, v of an attention layer in ONE grouped launch,
+    and gate+up with SwiGLU fused into the epilogue (interleaved columns, [m, 9216] output).  Algorithmic bytes are
+    those of the separate GEMMs (the SwiGLU row writes half the output columns)."""
+    import kiln_b200
+    from kiln_b200 import MarlinPackedProj
+
+    t = d.torch
+    out = {}
+    k = 2560
+    copies = 24
+    qkv = [[MarlinPackedProj(b, s, 128, k, n) for (b, s) in d.weights(k, n, copies)] for n in (4096, 512, 512)]
+    gu_copies = 14
+    gu = [MarlinPackedProj(b, s, 128, k, 18432) for (b, s) in d.weights(k, 18432, gu_copies)]
+    for m in (1, 16):
+        a = d.acts(m, k)
+        outs = [t.empty((m, n), dtype=t.bfloat16, device=d.dev) for n in (4096, 512, 512)]
+        nl = 48
+
+        def fn():
+            for i in range(nl):
+                kiln_b200.grouped_matmul_bf16([a, a, a], [qkv[0][i % copies], qkv[1][i % copies], qkv[2][i % copies]], outs)
+
+        us = d.time_graph(fn, nl, reps=7)
+        by = sum(alg_bytes(m, k, n) for n in (4096, 512, 512)) - 2 * m * k * 2  # the activations are read once
+        out[f"qkv_grouped:m{m}"] = {"us": round(us, 2), "GBps": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4),
+                                    "launches": 1}
+        o2 = t.empty((m, 9216), dtype=t.bfloat16, device=d.dev)
+
+        def fn2():
+            for i in range(nl):
+                kiln_b200.swiglu_gate_up(a, gu[i % gu_copies], out=o2)
+
+        us = d.time_graph(fn2, nl, reps=7)
+        by = alg_bytes(m, k, 18432) - m * 9216 * 2
+        out[f"gate_up_swiglu:m{m}"] = {"us": round(us, 2), "GBps": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4)}
     return out
 
 

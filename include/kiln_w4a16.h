@@ -37,10 +37,10 @@ typedef int kiln_w4a16_status_t;
  * Differences, all removing work from the caller:
  *   - A [prob_m, prob_k] and C [prob_m, prob_n] are bf16 (the reference kernel is
  *     fp16-only and its wrapper casts on both sides, lib.rs:169, 269);
- *   - `workspace` is scratch for split-K partial sums; it must hold at least
- *     kiln_w4a16_workspace_bytes(prob_m, prob_n, prob_k) bytes.  It needs no
- *     zero-initialisation and its contents after the call are unspecified.
- *     NULL is accepted when that function returns 0;
+ *   - `workspace` is never read or written: the reference's lock array of (prob_n / 128) * max_par int32
+ *     (lib.rs:174-178) may be passed unchanged, or NULL.  In exchange this entry point keeps the tcgen05
+ *     kernel to tilings without split-K or stream-K, which costs up to ~30 % at large prob_m on narrow
+ *     projections; kiln_w4a16_gemm_bf16, with a sized workspace, has no such limit;
  *   - `dev` is ignored: the launch goes to the device that owns `stream`'s context
  *     (the reference hard-codes ordinal 0, lib.rs:210-215);
  *   - thread_k / thread_n / sms / max_par are accepted for signature compatibility;
@@ -62,6 +62,50 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
                                          int n, int k, int groupsize, void *workspace,
                                          size_t workspace_bytes, void *stream);
 
+/* Epilogue options of kiln_w4a16_gemm_bf16_ex.  They fuse what the reference does in separate kernels after its
+ * Marlin call: the LoRA delta `x @ A^T @ B^T * scale` (crates/kiln-model/src/lora_loader.rs:213-233, added at
+ * crates/kiln-model/src/forward.rs:2935-2939) and, for the gate+up projection, SiLU and the elementwise product
+ * (forward.rs:2769-2839).
+ *   lora_a    bf16 [lora_rank, k], lora_b bf16 [n, lora_rank] (device, 16-byte aligned), lora_rank a multiple of 8 up to
+ *             128, lora_scale = alpha / rank.  The rank-r projection scale * x * A^T is computed first by a small kernel
+ *             into the workspace (fp32), the GEMM adds its product with B^T to the fp32 sums before rounding to bf16.
+ *   swiglu    1: the packed matrix holds the gate and up projections as ONE matrix whose columns alternate in runs of
+ *             32 (columns 64c .. 64c+31 are gate columns 32c .. 32c+31, columns 64c+32 .. 64c+63 the up columns of the
+ *             same indices; n = 2 * intermediate size).  C is then [m, n/2] = silu(gate) * up, computed in fp32 from the
+ *             unrounded sums (the reference rounds gate and up to bf16 first).  lora_b follows the same column order.
+ * For batch sizes the decode kernel serves (kiln_w4a16_workspace_bytes(m, n, k) == 0) the options are fused into that
+ * kernel's final reduction; for larger ones the plain GEMM result goes to the workspace and a second kernel applies them. */
+typedef struct kiln_w4a16_epilogue {
+    int swiglu;
+    const void *lora_a;
+    const void *lora_b;
+    int lora_rank;
+    float lora_scale;
+} kiln_w4a16_epilogue_t;
+
+/* kiln_w4a16_gemm_bf16 with epilogue options (NULL or all-zero options: the same call).  The workspace must hold
+ * kiln_w4a16_workspace_bytes_ex(m, n, k, ep) bytes.  New; the reference has no fused form. */
+size_t kiln_w4a16_workspace_bytes_ex(int m, int n, int k, const kiln_w4a16_epilogue_t *ep);
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_ex(const void *A, const void *B, void *C, const void *s, int m, int n, int k,
+                                            int groupsize, const kiln_w4a16_epilogue_t *ep, void *workspace,
+                                            size_t workspace_bytes, void *stream);
+
+/* Several independent GEMMs in one launch: sibling projections of one layer that the reference issues as separate
+ * Marlin calls (q, k, v: crates/kiln-model/src/forward.rs; gate and up: forward.rs:2769-2839).  The problems may
+ * differ in every argument.  When every problem is at a decode batch size (kiln_w4a16_workspace_bytes == 0) and all
+ * have either at most 8 rows or more than 8, ONE decode-kernel launch covers all their column blocks; otherwise the
+ * problems are launched one after another with the given workspace (sized for the largest).  count <= 8. */
+#define KILN_W4A16_MAX_GROUP 8
+typedef struct kiln_w4a16_problem {
+    const void *A;
+    const void *B;
+    void *C;
+    const void *s;
+    int m, n, k, groupsize;
+} kiln_w4a16_problem_t;
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_grouped(const kiln_w4a16_problem_t *problems, int count, void *workspace,
+                                                 size_t workspace_bytes, void *stream);
+
 /* No counterpart in the reference.  The same GEMM for callers that can neither allocate device
  * memory when they call nor lend a workspace: a server whose start-up gave all remaining HBM to
  * its KV-cache pool, or a serving loop that cannot take the device-wide synchronisation that
@@ -70,7 +114,8 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
  * a caller buffer.  Limits and rules:
  *   - the array is KILN_W4A16_NOALLOC_SCRATCH_BYTES (16 MiB) per GPU, held from library load to
  *     process exit; a problem whose split needs more (splits * m * n * 4 bytes) is refused with
- *     KILN_W4A16_ERR_STATIC_SCRATCH and nothing is launched;
+ *     KILN_W4A16_ERR_STATIC_SCRATCH and nothing is launched; the tiling is chosen among those that fit (a
+ *     tiling without a split always does), so in practice only a tiling forced through the tuning hook is refused;
  *   - the call makes no cudaMalloc, cudaFree or other allocating call.  The first call on each
  *     device looks up the array's device address (that device must be current) and sets the
  *     kernel's shared-memory attribute; make that first call before any stream capture;
@@ -78,10 +123,13 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
  *     Nothing in it needs clearing (each split overwrites its slab before it is read), but two
  *     calls that overlap on the same GPU (different streams) race on it: serialise them;
  *   - bounded-wait failures of these launches are recorded in a status word of the same kind
- *     inside the library image; kiln_w4a16_check_device_status does not read it. */
+ *     inside the library image; kiln_w4a16_check_device_status reads and clears it too. */
 #define KILN_W4A16_NOALLOC_SCRATCH_BYTES (16u << 20)
 kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const void *B, void *C, const void *s, int m,
                                                  int n, int k, int groupsize, void *stream);
+/* Diagnostic: the tiling that entry point uses for (m, n, k), as {bn, splits, m_tiles, stream_k}; splits > 1 means the
+ * built-in array is in use.  No counterpart in the reference. */
+void kiln_w4a16_noalloc_plan(int m, int n, int k, int out[4]);
 
 /* Column-parallel GEMM with the all-gather fused into its epilogue.  The reference is single-GPU (its
  * wrapper hard-codes device 0, crates/kiln-marlin-gemm/src/lib.rs:210-215); this replaces "GEMM on the local
@@ -166,9 +214,10 @@ kiln_w4a16_status_t kiln_w4a16_repack_gptq_device(const int32_t *qweight, const 
 /* Last CUDA error code seen by this library on the calling thread (0 = none). */
 int kiln_w4a16_last_cuda_error(void);
 
-/* Reads and clears the device status word that bounded device-side waits write
- * when they give up.  Synchronises `stream`.  Returns KILN_W4A16_OK or
- * KILN_W4A16_ERR_TIMEOUT; *detail (optional) receives the raw word. */
+/* Reads and clears the device status words that bounded device-side waits write
+ * when they give up (the one of the ordinary launches and the one of the no-allocation
+ * entry).  Synchronises `stream`.  Returns KILN_W4A16_OK or KILN_W4A16_ERR_TIMEOUT;
+ * *detail (optional) receives the raw word. */
 kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detail);
 
 /* Tuning hook for sweeps: force the decode kernel's decomposition (cluster size
@@ -192,6 +241,18 @@ void kiln_w4a16_set_prefill_min_m(int min_m);
  * restores the rule.  kiln_w4a16_workspace_bytes follows the override.  Process-wide, not thread-safe; no counterpart in
  * the reference. */
 void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k);
+
+/* How long a bounded device-side wait of the tcgen05 kernel polls before it gives up (nanoseconds; 0 restores the
+ * default of 400 ms).  When a wait gives up the kernel records a code, every other wait of the CTA stops, outstanding
+ * copies are drained, tensor memory is freed and the launch returns; kiln_w4a16_check_device_status then reports
+ * KILN_W4A16_ERR_TIMEOUT and the next launch starts clean.  Replaces the unbounded spin of the reference's barrier
+ * (crates/kiln-marlin-gemm/csrc/marlin_kernel.cu:162-171).  Process-wide, not thread-safe. */
+void kiln_w4a16_set_wait_limit_ns(unsigned long long ns);
+
+/* TEST HOOK for the give-up path above: the activation tile of K-step `k_step` (counted per CTA from 0) is announced
+ * to its barrier but never copied, so the wait for it runs out.  Nothing faults or spins past the limit.  -1 switches
+ * the hook off.  Process-wide, not thread-safe; no counterpart in the reference. */
+void kiln_w4a16_test_drop_activation_load(int k_step);
 
 /* Diagnostic: the tiling the tcgen05 kernel would use for (m, n, k) on the current device, as
  * out = {bn, splits, m_tiles, stream_k} (the arguments of kiln_w4a16_set_prefill_override). */

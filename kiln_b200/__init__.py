@@ -18,6 +18,11 @@ from .shard import (  # noqa: F401
 from .marlin_proj import (  # noqa: F401
     MarlinPackedProj,
     concat_projections,
+    interleave_gate_up,
+    interleave_columns_32,
+    swiglu_gate_up,
+    matmul_bf16_lora,
+    grouped_matmul_bf16,
     pack_from_gptq,
     PackedCache,
     matmul_bf16,
@@ -28,6 +33,6 @@ from .marlin_proj import (  # noqa: F401
 
 __all__ = [
     "pack", "marlin_w4a16_gemm", "workspace_bytes", "KilnMarlinError", "MarlinPackedProj",
-    "matmul_bf16", "concat_projections", "pack_from_gptq", "PackedCache", "pack_from_bf16", "pack_from_bf16_batch", "shape_is_supported",
+    "matmul_bf16", "concat_projections", "interleave_gate_up", "interleave_columns_32", "swiglu_gate_up", "matmul_bf16_lora", "grouped_matmul_bf16", "pack_from_gptq", "PackedCache", "pack_from_bf16", "pack_from_bf16_batch", "shape_is_supported",
     "ColumnParallelLinear", "FusedGatherOutput", "fused_column_parallel_gemm", "all_gather_columns", "shard_bounds", "shard_packed", "shard_proj",
 ]

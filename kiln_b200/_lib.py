@@ -29,11 +29,28 @@ STATUS_NAMES = {
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
+
+class Epilogue(ctypes.Structure):
+    """kiln_w4a16_epilogue_t."""
+
+    _fields_ = [("swiglu", _i), ("lora_a", _vp), ("lora_b", _vp), ("lora_rank", _i), ("lora_scale", ctypes.c_float)]
+
+
+class Problem(ctypes.Structure):
+    """kiln_w4a16_problem_t."""
+
+    _fields_ = [("A", _vp), ("B", _vp), ("C", _vp), ("s", _vp), ("m", _i), ("n", _i), ("k", _i), ("groupsize", _i)]
+
+
 # name -> (restype, argtypes); must list every symbol include/kiln_w4a16.h declares
 SIGNATURES = {
     "kiln_marlin_w4a16_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _i, _i, _i]),
     "kiln_w4a16_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "kiln_w4a16_workspace_bytes_ex": (_sz, [_i, _i, _i, ctypes.POINTER(Epilogue)]),
+    "kiln_w4a16_gemm_bf16_ex": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.POINTER(Epilogue), _vp, _sz, _vp]),
+    "kiln_w4a16_gemm_bf16_grouped": (_i, [ctypes.POINTER(Problem), _i, _vp, _sz, _vp]),
     "kiln_w4a16_gemm_bf16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "kiln_w4a16_noalloc_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "kiln_w4a16_gemm_bf16_allgather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp]),
     "kiln_w4a16_gemm_bf16_allgather_multicast": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "kiln_w4a16_workspace_bytes": (_sz, [_i, _i, _i]),
@@ -52,6 +69,8 @@ SIGNATURES = {
     "kiln_w4a16_set_decode_override": (None, [_i, _i, _i]),
     "kiln_w4a16_decode_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "kiln_w4a16_set_prefill_override": (None, [_i, _i, _i, _i]),
+    "kiln_w4a16_set_wait_limit_ns": (None, [ctypes.c_ulonglong]),
+    "kiln_w4a16_test_drop_activation_load": (None, [_i]),
     "kiln_w4a16_prefill_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "kiln_w4a16_set_prefill_min_m": (None, [_i]),
     "kiln_w4a16_version": (_i, []),

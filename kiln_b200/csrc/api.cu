@@ -91,7 +91,7 @@ static int gemm(const GemmArgs &a) {
     const int v = validate(a);
     if (v >= 0) return v;
     if (use_prefill(a.m, a.n, a.k, a.groupsize)) {
-        const size_t need = prefill_workspace_bytes(a.m, a.n, a.k);
+        const size_t need = a.no_scratch ? 0 : prefill_workspace_bytes(a.m, a.n, a.k);
         if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
         return launch_prefill(a);
     }
@@ -125,11 +125,13 @@ kiln_w4a16_status_t kiln_marlin_w4a16_gemm(const void *A, const void *B, void *C
         if (prob_n % thread_n != 0 || prob_k % thread_k != 0) return KILN_W4A16_ERR_PROB_SHAPE;
         if (!known) return KILN_W4A16_ERR_KERN_SHAPE;
     }
-    // The legacy signature carries no size: the contract is that the caller sized the
-    // buffer with kiln_w4a16_workspace_bytes().
-    const size_t need = kiln_w4a16_workspace_bytes(prob_m, prob_n, prob_k);
-    GemmArgs a{A, B, s, C, prob_m, prob_n, prob_k, groupsize, workspace, workspace ? need : 0,
-               static_cast<cudaStream_t>(stream)};
+    // The legacy signature carries no size, and an unmodified reference wrapper passes its lock array of
+    // (n / 128) * 16 int32 (kiln-marlin-gemm/src/lib.rs:174-178): this entry therefore never writes to `workspace`.  The
+    // tcgen05 kernel is restricted to tilings without split-K or stream-K here; the faster tilings need
+    // kiln_w4a16_gemm_bf16, whose workspace size is checked.
+    (void)workspace;
+    GemmArgs a{A, B, s, C, prob_m, prob_n, prob_k, groupsize, nullptr, 0, static_cast<cudaStream_t>(stream)};
+    a.no_scratch = true;
     return gemm(a);
 }
 
@@ -167,6 +169,90 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather_multicast(const void *A, cons
     return launch_prefill(a);
 }
 
+namespace {
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+int validate_epilogue(const kiln_w4a16_epilogue_t *ep, int n) {
+    if (!ep) return KILN_W4A16_OK;
+    if (ep->swiglu && n % 128 != 0) return KILN_W4A16_ERR_PROB_SHAPE;
+    if (ep->lora_rank < 0 || ep->lora_rank > 128 || ep->lora_rank % 8 != 0) return KILN_W4A16_ERR_ARG;
+    if (ep->lora_rank && (!ep->lora_a || !ep->lora_b)) return KILN_W4A16_ERR_ARG;
+    if (ep->lora_rank && ((reinterpret_cast<uintptr_t>(ep->lora_a) | reinterpret_cast<uintptr_t>(ep->lora_b)) & 15))
+        return KILN_W4A16_ERR_ALIGNMENT;
+    return KILN_W4A16_OK;
+}
+}  // namespace
+
+size_t kiln_w4a16_workspace_bytes_ex(int m, int n, int k, const kiln_w4a16_epilogue_t *ep) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    const bool opts = ep && (ep->swiglu || ep->lora_rank);
+    if (!opts) return kiln_w4a16_workspace_bytes(m, n, k);
+    size_t need = align256(static_cast<size_t>(m) * ep->lora_rank * sizeof(float));
+    if (use_prefill(m, n, k, 128))  // not fused at this batch size yet: base result + the tcgen05 kernel's own scratch
+        need += align256(static_cast<size_t>(m) * n * 2) + align256(prefill_workspace_bytes(m, n, k));
+    return need;
+}
+
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_ex(const void *A, const void *B, void *C, const void *s, int m, int n, int k,
+                                            int groupsize, const kiln_w4a16_epilogue_t *ep, void *workspace,
+                                            size_t workspace_bytes, void *stream) {
+    const bool opts = ep && (ep->swiglu || ep->lora_rank);
+    if (!opts) return kiln_w4a16_gemm_bf16(A, B, C, s, m, n, k, groupsize, workspace, workspace_bytes, stream);
+    if (int rc = validate_epilogue(ep, n)) return rc;
+    GemmArgs a{A, B, s, C, m, n, k, groupsize, workspace, workspace_bytes, static_cast<cudaStream_t>(stream)};
+    const int v = validate(a);
+    if (v >= 0) return v;
+    const size_t need = kiln_w4a16_workspace_bytes_ex(m, n, k, ep);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    float *t = nullptr;
+    if (ep->lora_rank) {
+        t = reinterpret_cast<float *>(ws);
+        ws += align256(static_cast<size_t>(m) * ep->lora_rank * sizeof(float));
+        if (int rc = launch_lora_down(A, ep->lora_a, ep->lora_scale, m, k, ep->lora_rank, t, a.stream)) return rc;
+    }
+    if (!use_prefill(m, n, k, groupsize)) {
+        a.lora_t = t;
+        a.lora_b = ep->lora_b;
+        a.lora_r = ep->lora_rank;
+        a.swiglu = ep->swiglu ? 1 : 0;
+        return launch_decode(a, g_decode_override);
+    }
+    void *tmp = ws;
+    ws += align256(static_cast<size_t>(m) * n * 2);
+    GemmArgs b{A, B, s, tmp, m, n, k, groupsize, ws, prefill_workspace_bytes(m, n, k), a.stream};
+    if (int rc = launch_prefill(b)) return rc;
+    return launch_finish(tmp, C, m, n, t, ep->lora_b, ep->lora_rank, ep->swiglu ? 1 : 0, a.stream);
+}
+
+kiln_w4a16_status_t kiln_w4a16_gemm_bf16_grouped(const kiln_w4a16_problem_t *problems, int count, void *workspace,
+                                                 size_t workspace_bytes, void *stream) {
+    if (!problems || count < 1 || count > KILN_W4A16_MAX_GROUP) return KILN_W4A16_ERR_ARG;
+    DecodeItem items[KILN_W4A16_MAX_GROUP] = {};
+    bool one_launch = true;
+    int live = 0;
+    for (int i = 0; i < count; ++i) {
+        const kiln_w4a16_problem_t &q = problems[i];
+        GemmArgs a{q.A, q.B, q.s, q.C, q.m, q.n, q.k, q.groupsize, workspace, workspace_bytes, static_cast<cudaStream_t>(stream)};
+        const int v = validate(a);
+        if (v > 0) return v;
+        if (v == 0) continue;  // an empty problem
+        if (use_prefill(q.m, q.n, q.k, q.groupsize)) one_launch = false;
+        items[live++] = DecodeItem{q.A, q.B, q.s, q.C, q.m, q.n, q.k, q.groupsize, nullptr, nullptr, 0, 0};
+    }
+    if (live == 0) return KILN_W4A16_OK;
+    // one batch class per launch: up to 8 rows, or 9 and more
+    for (int i = 1; i < live; ++i)
+        if ((items[i].m <= 8) != (items[0].m <= 8)) one_launch = false;
+    if (one_launch) return launch_decode_list(items, live, static_cast<cudaStream_t>(stream), g_decode_override);
+    for (int i = 0; i < live; ++i) {  // batch sizes of the tcgen05 kernel, or mixed classes: one launch each
+        const DecodeItem &q = items[i];
+        if (int rc = kiln_w4a16_gemm_bf16(q.A, q.B, q.C, q.S, q.m, q.n, q.k, q.groupsize, workspace, workspace_bytes, stream))
+            return rc;
+    }
+    return KILN_W4A16_OK;
+}
+
 size_t kiln_w4a16_workspace_bytes(int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
     if (use_prefill(m, n, k, 128)) return prefill_workspace_bytes(m, n, k);
@@ -184,13 +270,14 @@ kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detai
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (int rc = record_cuda_error(cudaMemcpyAsync(&host, w, sizeof(host), cudaMemcpyDeviceToHost, st))) return rc;
     if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
-    if (detail) *detail = host;
+    uint32_t host_static = 0;  // the word of the no-allocation entry's launches (kept in the library image)
+    if (int rc = static_status_read_clear(st, &host_static)) return rc;
+    if (detail) *detail = host ? host : host_static;
     if (host != 0) {
         if (int rc = record_cuda_error(cudaMemsetAsync(w, 0, sizeof(uint32_t), st))) return rc;
         if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
-        return KILN_W4A16_ERR_TIMEOUT;
     }
-    return KILN_W4A16_OK;
+    return (host | host_static) ? KILN_W4A16_ERR_TIMEOUT : KILN_W4A16_OK;
 }
 
 void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n) {
@@ -204,6 +291,10 @@ void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]) {
 void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k) {
     set_prefill_override(bn, splits, m_tiles, stream_k);
 }
+
+void kiln_w4a16_set_wait_limit_ns(unsigned long long ns) { set_wait_limit_ns(ns); }
+
+void kiln_w4a16_test_drop_activation_load(int k_step) { set_test_drop_a_load(k_step); }
 
 void kiln_w4a16_prefill_plan(int m, int n, int k, int out[4]) {
     if (out) prefill_plan(m, n, k, out);

@@ -27,28 +27,46 @@
 //    order, so results are bit-reproducible.
 //  * nothing in this kernel polls: the only waits are `bar.sync`, the cluster barrier (both reached by every
 //    thread on every path) and `griddepcontrol.wait`.
+#include <algorithm>
+
 #include "w4a16_common.cuh"
 
 namespace kiln {
 namespace {
 
-struct DecodeParams {
+constexpr int kMaxProblems = 8;  // GEMMs one launch may cover (kiln_w4a16_gemm_bf16_grouped)
+
+// One GEMM of a launch.  A launch covers up to kMaxProblems independent GEMMs that share the decomposition
+// (cluster size, warps per CTA) and differ in everything else; blockIdx.y runs over the column blocks of all of them.
+struct DecodeProblem {
     const __nv_bfloat16 *A;
     const uint4 *B;  // packed weights as 16-byte pieces: [k/16][n/64][32 lanes]
     const __half *S;
     __nv_bfloat16 *C;
+    const float *lora_t;           // fp32 [m, lora_r] = scale * x * A^T, or null: no LoRA delta
+    const __nv_bfloat16 *lora_b;   // bf16 [n, lora_r]
     int m, n, k;
     int groups;          // k / 128
     int groups_per_cta;  // K groups owned by one CTA of the cluster
     int pass_groups;     // K groups whose activations are staged in shared memory at a time
+    int per_column;      // groupsize == -1: one scale row, applied at the end
+    int a_pitch;         // bytes per staged activation row (pass_groups*256 + 16)
+    int y0;              // first blockIdx.y of this problem
+    int lora_r;          // LoRA rank (multiple of 8, 0 = none)
+    int swiglu;          // columns hold gate and up interleaved in runs of 32; C is [m, n/2] = silu(gate) * up
+};
+
+struct DecodeParams {
+    DecodeProblem prob[kMaxProblems];
+    int count;
     int warps_n, warps_k;
-    int per_column;  // groupsize == -1: one scale row, applied at the end
-    int a_pitch;     // bytes per staged activation row (pass_groups*256 + 16)
-    int red_pitch;   // floats per reduction row (warps_n*64 + 4 or 8)
-    int off_red, off_recv;  // shared-memory carve-up (bytes from the 128-byte aligned base)
+    int red_pitch;          // floats per reduction row (warps_n*64 + 4 or 8)
+    int off_red, off_recv, off_lora;  // shared-memory carve-up (bytes from the 128-byte aligned base)
     int ppr_shift;          // log2 of the output pairs (two adjacent columns) per row of a CTA = 5 + log2(warps_n)
-    int own_cols;           // pairs per row owned by one rank of the cluster = ceil(pairs per row / cluster size)
+    int own_cols;           // receive slots per row owned by one rank of the cluster
     uint32_t own_magic;     // ceil(2^32 / own_cols): x / own_cols = umulhi(x, own_magic) for the small x used here
+    int own_items;          // SwiGLU: (gate pair, up pair) items per row owned by one rank = own_cols / 2
+    uint32_t item_magic;    // ceil(2^32 / own_items)
 };
 
 constexpr uint32_t kLoMask = 0x000F000Fu, kHiMask = 0x00F000F0u;
@@ -210,10 +228,12 @@ __device__ __forceinline__ void compute_unit_s(uint4 (&w)[8], const uint4 *next,
 
 constexpr uint4 kOnesF16 = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 
-// grid = (cluster_k, n / (64*warps_n), ceil(m / (8*NB))), cluster = (cluster_k, 1, 1),
+// grid = (cluster_k, sum over problems of n / (64*warps_n), ceil(max m / (8*NB))), cluster = (cluster_k, 1, 1),
 // block = 32 * warps_n * warps_k: warp wk*warps_n + wn streams chunk wn of the groups i with i % warps_k == wk.
-template <int NB>
-__global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_decode_kernel(const DecodeParams p) {
+// MULTI: the launch covers several GEMMs (the lookup below and the indexed parameter reads cost a single large GEMM a few
+// per cent, so single-GEMM launches use the other instance).
+template <int NB, bool MULTI>
+__global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_decode_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     uint8_t *base_gen = smem_raw + (base - smem_u32(smem_raw));
@@ -221,6 +241,15 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
 
     pdl_launch_dependents();
     constexpr int kRows = 8 * NB;
+    // which GEMM of the launch this CTA works on (every CTA of a cluster shares blockIdx.y and .z)
+    int pi = 0;
+    if (MULTI) {
+#pragma unroll
+        for (int i = 1; i < kMaxProblems; ++i)
+            if (i < p.count && static_cast<int>(blockIdx.y) >= p.prob[i].y0) pi = i;
+    }
+    const DecodeProblem &q = p.prob[pi];
+    if (static_cast<int>(blockIdx.z) * kRows >= q.m) return;  // a GEMM with fewer rows than the tallest of the launch
     Acc<NB> acc;
 #pragma unroll
     for (int j = 0; j < 4 * NB; ++j)
@@ -235,23 +264,23 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthreads = blockDim.x;
     const int m0 = blockIdx.z * kRows;
-    const int m_valid = min(kRows, p.m - m0);
+    const int m_valid = min(kRows, q.m - m0);
     const int wn = warp % p.warps_n, wk = warp / p.warps_n;
-    const int chunk = blockIdx.y * p.warps_n + wn;
-    const int gc0 = min(p.groups, static_cast<int>(rank) * p.groups_per_cta);
-    const int gc1 = min(p.groups, gc0 + p.groups_per_cta);
+    const int chunk = (static_cast<int>(blockIdx.y) - q.y0) * p.warps_n + wn;
+    const int gc0 = min(q.groups, static_cast<int>(rank) * q.groups_per_cta);
+    const int gc1 = min(q.groups, gc0 + q.groups_per_cta);
     const int nst = gc1 - gc0;  // K groups of this CTA
     const int qd = lane & 3, c = lane >> 2;
 
     // ---- this warp's stream: local groups wk, wk + warps_k, ... of chunk `chunk` ----
-    const uint32_t chunks = static_cast<uint32_t>(p.n >> 6);
+    const uint32_t chunks = static_cast<uint32_t>(q.n >> 6);
     const uint32_t kt_stride = chunks * 32;                // 16-byte pieces between K-tiles
     const uint32_t unit_stride = kt_stride * 8 * p.warps_k;  // ... between this warp's units
-    const uint4 *wptr = p.B + (static_cast<size_t>(gc0 + wk) * 8 * chunks + chunk) * 32 + lane;
+    const uint4 *wptr = q.B + (static_cast<size_t>(gc0 + wk) * 8 * chunks + chunk) * 32 + lane;
     // scales of a unit: NB = 1 needs the 16 bytes at position 8c of the chunk's scale order (columns c + 8t),
     // NB = 2 the 32 bytes at 16qd (columns 8t + 2qd and 8t + 2qd + 1)
-    const uint32_t s_unit_stride = static_cast<uint32_t>(p.n) * p.warps_k / 8;
-    const uint4 *sptr = reinterpret_cast<const uint4 *>(p.S + static_cast<size_t>(gc0 + wk) * p.n + chunk * 64) +
+    const uint32_t s_unit_stride = static_cast<uint32_t>(q.n) * p.warps_k / 8;
+    const uint4 *sptr = reinterpret_cast<const uint4 *>(q.S + static_cast<size_t>(gc0 + wk) * q.n + chunk * 64) +
                         (NB == 1 ? c : 2 * qd);
     uint4 w[8];
     uint4 sc0 = kOnesF16, sc1 = kOnesF16;
@@ -260,10 +289,18 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
     if (gl < nst) {
 #pragma unroll
         for (int kt = 0; kt < 8; ++kt) w[kt] = ld_stream_v4(wptr + kt * kt_stride);
-        if (!p.per_column) {
+        if (!q.per_column) {
             sc0 = ld_stream_v4(sptr);
             if (NB == 2) sc1 = ld_stream_v4(sptr + 1);
         }
+    }
+    // LoRA: the rows of B^T for this CTA's columns are weights too; they land in shared memory asynchronously
+    if (q.lora_r) {
+        const int ppb = q.lora_r >> 3;  // 16-byte pieces per row of lora_b
+        const int cols = 64 * p.warps_n;
+        const __nv_bfloat16 *src = q.lora_b + static_cast<size_t>(chunk - wn) * 64 * q.lora_r;
+        for (int idx = tid; idx < cols * ppb; idx += nthreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + p.off_lora + idx * 16), "l"(src + idx * 8) : "memory");
     }
 
     // lane-constant part of the ldmatrix address.  NB = 1 (x2): lanes 0-7 address rows 0-7 at K+0, lanes 8-15 the
@@ -272,23 +309,23 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
     // accumulator rows that are never stored).
     uint32_t a_lane;
     if (NB == 1) {
-        a_lane = sA + static_cast<uint32_t>(min(lane & 7, m_valid - 1)) * p.a_pitch + static_cast<uint32_t>((lane >> 3) & 1) * 16u;
+        a_lane = sA + static_cast<uint32_t>(min(lane & 7, m_valid - 1)) * q.a_pitch + static_cast<uint32_t>((lane >> 3) & 1) * 16u;
     } else {
-        a_lane = sA + static_cast<uint32_t>(min((lane & 7) + ((lane >> 3) & 1) * 8, m_valid - 1)) * p.a_pitch +
+        a_lane = sA + static_cast<uint32_t>(min((lane & 7) + ((lane >> 3) & 1) * 8, m_valid - 1)) * q.a_pitch +
                  static_cast<uint32_t>(lane >> 4) * 16u;
     }
 
     // Activation staging.  The addresses of a thread's first 16-byte piece are formed here, before the wait, so that
     // after it only load -> convert -> store -> barrier remain.
-    const int ppr_a = min(p.pass_groups, nst) * 16;  // 16-byte pieces per row in the first pass
-    const __nv_bfloat16 *a_base = p.A + static_cast<size_t>(m0) * p.k + static_cast<size_t>(gc0) * kGroup;
+    const int ppr_a = min(q.pass_groups, nst) * 16;  // 16-byte pieces per row in the first pass
+    const __nv_bfloat16 *a_base = q.A + static_cast<size_t>(m0) * q.k + static_cast<size_t>(gc0) * kGroup;
     const uint4 *a_src0;
     uint32_t a_dst0;
     {
         const int r0 = m_valid == 1 ? 0 : tid / max(ppr_a, 1);
         const int c0 = tid - r0 * ppr_a;
-        a_src0 = reinterpret_cast<const uint4 *>(a_base + static_cast<size_t>(r0) * p.k + c0 * 8);
-        a_dst0 = sA + r0 * p.a_pitch + c0 * 16;
+        a_src0 = reinterpret_cast<const uint4 *>(a_base + static_cast<size_t>(r0) * q.k + c0 * 8);
+        a_dst0 = sA + r0 * q.a_pitch + c0 * 16;
     }
     auto convert_store = [](uint32_t dst, const uint4 &v) {
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(bf16x2_to_f16x2(v.x)), "r"(bf16x2_to_f16x2(v.y)),
@@ -298,9 +335,16 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
 
     // Everything below reads A or writes C: order it after the previous kernel in the stream.
     pdl_wait();
+    if (q.lora_r) {  // scale * x * A^T of this CTA's rows (written by the kernel before this one)
+        const int pieces = m_valid * (q.lora_r >> 2);
+        const float *src = q.lora_t + static_cast<size_t>(m0) * q.lora_r;
+        const uint32_t dst = base + p.off_lora + 64 * p.warps_n * q.lora_r * 2;
+        for (int idx = tid; idx < pieces; idx += nthreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + idx * 16), "l"(src + idx * 4) : "memory");
+    }
 
-    for (int pg0 = 0; pg0 < nst; pg0 += p.pass_groups) {
-        const int plen = min(p.pass_groups, nst - pg0);
+    for (int pg0 = 0; pg0 < nst; pg0 += q.pass_groups) {
+        const int plen = min(q.pass_groups, nst - pg0);
         if (pg0 > 0) __syncthreads();  // everyone is done with the previous pass' activations
         // ---- stage A[m0 .. m0+m_valid, (gc0+pg0)*128 .. +plen*128) as fp16 ----
         // A thread's first piece of the first pass goes load -> convert -> store (shortest path: its addresses were
@@ -313,8 +357,8 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
             const __nv_bfloat16 *a_src = a_base + static_cast<size_t>(pg0) * kGroup;
             for (int idx = first; idx < total; idx += nthreads) {
                 const int r = idx / ppr, pc = idx - r * ppr;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sA + r * p.a_pitch + pc * 16),
-                             "l"(a_src + static_cast<size_t>(r) * p.k + pc * 8)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sA + r * q.a_pitch + pc * 16),
+                             "l"(a_src + static_cast<size_t>(r) * q.k + pc * 8)
                              : "memory");
             }
             if (pg0 == 0 && tid < total) convert_store(a_dst0, ld_cg_v4(a_src0));
@@ -322,7 +366,7 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 for (int idx = first; idx < total; idx += nthreads) {
                     const int r = idx / ppr, pc = idx - r * ppr;
-                    const uint32_t addr = sA + r * p.a_pitch + pc * 16;
+                    const uint32_t addr = sA + r * q.a_pitch + pc * 16;
                     convert_store(addr, lds_v4(addr));
                 }
             }
@@ -340,13 +384,12 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
             wptr = next;
             sptr += s_unit_stride;
             // the next unit's scales are needed only after its eight K-tiles: request them now
-            if (more && !p.per_column) {
+            if (more && !q.per_column) {
                 sc0 = ld_stream_v4(sptr);
                 if (NB == 2) sc1 = ld_stream_v4(sptr + 1);
             }
         }
     }
-
     }  // streaming part
     // ---- this warp's partial tile -> shared memory ----
     // Thread and block coordinates are read again here (volatile reads cannot be merged with the earlier ones), so
@@ -359,7 +402,7 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
     const int qd = lane & 3, c = lane >> 2;
     const int wn = warp % p.warps_n, wk = warp / p.warps_n;
     const int m0 = static_cast<int>(bz_v) * kRows;
-    const int m_valid = min(kRows, p.m - m0);
+    const int m_valid = min(kRows, q.m - m0);
     const int nthreads = blockDim.x;
     const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
     float *sRed = reinterpret_cast<float *>(base_gen + p.off_red);
@@ -383,32 +426,22 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
             }
         }
     }
+    if (q.lora_r) asm volatile("cp.async.wait_all;" ::: "memory");  // this thread's pieces of lora_b and lora_t
     __syncthreads();
 
     // ---- reduction over the K-teams of the CTA, then over the CTAs of the cluster -----------
     // An output pair is two adjacent columns of one row.  The pairs of a row are dealt to the cluster ranks in
-    // contiguous slices of `own_cols`.  Every CTA sums its K-teams and pushes each pair into the owning rank's receive
-    // buffer, slot [sender rank][row][pair]; after ONE cluster barrier the owner adds the slots in rank order and
-    // writes C.  Nobody touches a peer's shared memory after that barrier, so CTAs may exit without a second one.
-    // Everything here is a chain of dependent instructions in few threads, so it avoids divisions and keeps the
-    // shared-memory loads of a sum independent of each other.
+    // contiguous slices (SwiGLU: slices of items, an item being a gate pair and the up pair 32 columns after it, so
+    // that both meet in one rank).  Every CTA sums its K-teams and pushes each pair into the owning rank's receive
+    // buffer, slot [sender rank][row][slot of the pair]; after ONE cluster barrier the owner adds the slots in rank
+    // order, finishes the values (per-column scale, LoRA delta, SwiGLU) and writes C.  Nobody touches a peer's
+    // shared memory after that barrier, so CTAs may exit without a second one.  Everything here is a chain of
+    // dependent instructions in few threads, so it avoids divisions and keeps the shared-memory loads of a sum
+    // independent of each other.
     const int ppr_shift = p.ppr_shift, ppr = 1 << ppr_shift;
-    const int npairs = m_valid << ppr_shift;
-    const int n0 = static_cast<int>(by_v) * (2 * ppr);
+    const int n0 = (static_cast<int>(by_v) - q.y0) * (2 * ppr);  // first column of this CTA within its GEMM
     const size_t team_stride = static_cast<size_t>(kRows) * p.red_pitch;
-    auto store_pair = [&](int row, int cp, float2 v) {
-        const int col = n0 + 2 * cp;
-        if (p.per_column) {
-            const int pos = scale_single_pos(col);  // col is even: col+1 sits at pos+1
-            v.x *= __half2float(p.S[pos]);
-            v.y *= __half2float(p.S[pos + 1]);
-        }
-        *reinterpret_cast<__nv_bfloat162 *>(p.C + static_cast<size_t>(m0 + row) * p.n + col) = __floats2bfloat162_rn(v.x, v.y);
-    };
-    const uint32_t recv_base = base + p.off_recv;
-    if (csize > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    for (int idx = tid; idx < npairs; idx += nthreads) {
-        const int row = idx >> ppr_shift, cp = idx & (ppr - 1);
+    auto team_sum = [&](int row, int cp) {
         const float *src = sRed + row * p.red_pitch + 2 * cp;
         float2 v = *reinterpret_cast<const float2 *>(src);
 #pragma unroll 4
@@ -417,25 +450,84 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
             v.x += u.x;
             v.y += u.y;
         }
-        if (csize > 1) {
-            const uint32_t owner = __umulhi(static_cast<uint32_t>(cp), p.own_magic);
-            const uint32_t j = cp - owner * p.own_cols;
-            st_dsmem_f2(map_to_cta(recv_base + 8u * ((rank * kRows + row) * p.own_cols + j), owner), v);
-        } else {
-            store_pair(row, cp, v);
+        return v;
+    };
+    // complete sums of a pair -> final values: per-column scale, then the LoRA delta of the two columns
+    auto finish_pair = [&](int row, int cp, float2 v) {
+        const int col = n0 + 2 * cp;
+        if (q.per_column) {
+            const int pos = scale_single_pos(col);  // col is even: col+1 sits at pos+1
+            v.x *= __half2float(q.S[pos]);
+            v.y *= __half2float(q.S[pos + 1]);
         }
+        if (q.lora_r) {
+            const uint4 *b0 = reinterpret_cast<const uint4 *>(base_gen + p.off_lora + static_cast<size_t>(2 * cp) * q.lora_r * 2);
+            const uint4 *b1 = b0 + (q.lora_r >> 3);
+            const float4 *t = reinterpret_cast<const float4 *>(base_gen + p.off_lora + 64 * p.warps_n * q.lora_r * 2 +
+                                                               static_cast<size_t>(row) * q.lora_r * 4);
+            float d0 = 0.f, d1 = 0.f;
+            for (int j = 0; j < (q.lora_r >> 3); ++j) {
+                const uint4 x0 = b0[j], x1 = b1[j];
+                const float4 ta = t[2 * j], tb = t[2 * j + 1];
+                d0 += ta.x * __uint_as_float(x0.x << 16) + ta.y * __uint_as_float(x0.x & 0xFFFF0000u) +
+                      ta.z * __uint_as_float(x0.y << 16) + ta.w * __uint_as_float(x0.y & 0xFFFF0000u) +
+                      tb.x * __uint_as_float(x0.z << 16) + tb.y * __uint_as_float(x0.z & 0xFFFF0000u) +
+                      tb.z * __uint_as_float(x0.w << 16) + tb.w * __uint_as_float(x0.w & 0xFFFF0000u);
+                d1 += ta.x * __uint_as_float(x1.x << 16) + ta.y * __uint_as_float(x1.x & 0xFFFF0000u) +
+                      ta.z * __uint_as_float(x1.y << 16) + ta.w * __uint_as_float(x1.y & 0xFFFF0000u) +
+                      tb.x * __uint_as_float(x1.z << 16) + tb.y * __uint_as_float(x1.z & 0xFFFF0000u) +
+                      tb.z * __uint_as_float(x1.w << 16) + tb.w * __uint_as_float(x1.w & 0xFFFF0000u);
+            }
+            v.x += d0;
+            v.y += d1;
+        }
+        return v;
+    };
+    auto store_pair = [&](int row, int cp, float2 v) {
+        *reinterpret_cast<__nv_bfloat162 *>(q.C + static_cast<size_t>(m0 + row) * q.n + n0 + 2 * cp) = __floats2bfloat162_rn(v.x, v.y);
+    };
+    // SwiGLU item `it` of a row: gate pair (it/16)*32 + it%16, up pair 16 further; output columns n0/2 + 2*it, +1
+    auto store_item = [&](int row, int it, float2 g, float2 u) {
+        const float ox = g.x / (1.f + __expf(-g.x)) * u.x, oy = g.y / (1.f + __expf(-g.y)) * u.y;
+        *reinterpret_cast<__nv_bfloat162 *>(q.C + static_cast<size_t>(m0 + row) * (q.n >> 1) + (n0 >> 1) + 2 * it) =
+            __floats2bfloat162_rn(ox, oy);
+    };
+    if (csize == 1) {
+        if (!q.swiglu) {
+            for (int idx = tid; idx < (m_valid << ppr_shift); idx += nthreads) {
+                const int row = idx >> ppr_shift, cp = idx & (ppr - 1);
+                store_pair(row, cp, finish_pair(row, cp, team_sum(row, cp)));
+            }
+        } else {
+            for (int idx = tid; idx < (m_valid << (ppr_shift - 1)); idx += nthreads) {
+                const int row = idx >> (ppr_shift - 1), it = idx & ((ppr >> 1) - 1);
+                const int cg = ((it >> 4) << 5) + (it & 15);
+                store_item(row, it, finish_pair(row, cg, team_sum(row, cg)), finish_pair(row, cg + 16, team_sum(row, cg + 16)));
+            }
+        }
+        return;
     }
-    if (csize == 1) return;
+    const uint32_t recv_base = base + p.off_recv;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    for (int idx = tid; idx < (m_valid << ppr_shift); idx += nthreads) {
+        const int row = idx >> ppr_shift, cp = idx & (ppr - 1);
+        const float2 v = team_sum(row, cp);
+        uint32_t owner, j;
+        if (!q.swiglu) {
+            owner = __umulhi(static_cast<uint32_t>(cp), p.own_magic);
+            j = cp - owner * p.own_cols;
+        } else {
+            const uint32_t it = static_cast<uint32_t>(((cp >> 5) << 4) + (cp & 15));
+            owner = __umulhi(it, p.item_magic);
+            j = 2 * (it - owner * p.own_items) + ((cp >> 4) & 1);
+        }
+        st_dsmem_f2(map_to_cta(recv_base + 8u * ((rank * kRows + row) * p.own_cols + j), owner), v);
+    }
     cluster_sync_all();
     {
         const float2 *recv = reinterpret_cast<const float2 *>(base_gen + p.off_recv);
-        const int cp0 = static_cast<int>(rank) * p.own_cols;
-        const int mine = min(p.own_cols, ppr - cp0);  // pairs per row this rank owns (none for a trailing rank)
         const int slot_stride = kRows * p.own_cols;
-        for (int idx = tid; idx < m_valid * p.own_cols; idx += nthreads) {
-            const int row = static_cast<int>(__umulhi(static_cast<uint32_t>(idx), p.own_magic));
-            const int j = idx - row * p.own_cols;
-            if (j >= mine) continue;
+        auto rank_sum = [&](int row, int j) {
             const float2 *src = recv + row * p.own_cols + j;
             float2 v = src[0];
 #pragma unroll 4
@@ -444,11 +536,30 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
                 v.x += u.x;
                 v.y += u.y;
             }
-            store_pair(row, cp0 + j, v);
+            return v;
+        };
+        if (!q.swiglu) {
+            const int cp0 = static_cast<int>(rank) * p.own_cols;
+            const int mine = min(p.own_cols, ppr - cp0);  // pairs per row this rank owns (none for a trailing rank)
+            for (int idx = tid; idx < m_valid * p.own_cols; idx += nthreads) {
+                const int row = static_cast<int>(__umulhi(static_cast<uint32_t>(idx), p.own_magic));
+                const int j = idx - row * p.own_cols;
+                if (j >= mine) continue;
+                store_pair(row, cp0 + j, finish_pair(row, cp0 + j, rank_sum(row, j)));
+            }
+        } else {
+            const int it0 = static_cast<int>(rank) * p.own_items;
+            const int mine = min(p.own_items, (ppr >> 1) - it0);
+            for (int idx = tid; idx < m_valid * p.own_items; idx += nthreads) {
+                const int row = static_cast<int>(__umulhi(static_cast<uint32_t>(idx), p.item_magic));
+                const int jj = idx - row * p.own_items;
+                if (jj >= mine) continue;
+                const int it = it0 + jj, cg = ((it >> 4) << 5) + (it & 15);
+                store_item(row, it, finish_pair(row, cg, rank_sum(row, 2 * jj)), finish_pair(row, cg + 16, rank_sum(row, 2 * jj + 1)));
+            }
         }
     }
 }
-
 
 // ---- host: decomposition heuristic and launch ---------------------------------------------
 
@@ -542,40 +653,53 @@ DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
     return c;
 }
 
-template <int NB>
-int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t stream) {
+template <int NB, bool MULTI>
+int launch_list(DecodeParams &p, int ck, int max_m, cudaStream_t stream) {
     static bool attr_set[64] = {};
-    constexpr int kMaxSmem = 160 * 1024;
+    constexpr int kMaxSmem = 200 * 1024;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
         if (int rc = record_cuda_error(
-                cudaFuncSetAttribute(w4a16_decode_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)))
+                cudaFuncSetAttribute(w4a16_decode_kernel<NB, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem)))
             return rc;
         attr_set[dev] = true;
     }
-    // carve-up: [A rows][reduction tiles][receive slots]
+    // carve-up: [A rows][reduction tiles][receive slots][LoRA: rows of B^T, then scale * x * A^T]
     auto align = [](int x, int a) { return (x + a - 1) / a * a; };
-    const int rows = m < 8 * NB ? m : 8 * NB;
-    p.a_pitch = c.pass_groups * 256 + 16;
-    p.red_pitch = c.warps_n * 64 + (NB == 1 ? 4 : 8);  // bank-conflict-free partial stores
-    p.off_red = align(rows * p.a_pitch, 128);
-    p.off_recv = p.off_red + align(static_cast<int>(sizeof(float)) * c.warps_k * 8 * NB * p.red_pitch, 128);
-    const int ppr = 32 * c.warps_n;  // a power of two: warps_n is 1, 2, 4 or 8
+    int a_bytes = 0, lora_bytes = 0, grid_y = 0;
+    bool swiglu = false;
+    for (int i = 0; i < p.count; ++i) {
+        DecodeProblem &q = p.prob[i];
+        const int rows = q.m < 8 * NB ? q.m : 8 * NB;
+        q.a_pitch = q.pass_groups * 256 + 16;
+        a_bytes = std::max(a_bytes, rows * q.a_pitch);
+        if (q.lora_r) lora_bytes = std::max(lora_bytes, 64 * p.warps_n * q.lora_r * 2 + 8 * NB * q.lora_r * 4);
+        swiglu |= q.swiglu != 0;
+        q.y0 = grid_y;
+        grid_y += q.n / (kChunkCols * p.warps_n);
+    }
+    p.red_pitch = p.warps_n * 64 + (NB == 1 ? 4 : 8);  // bank-conflict-free partial stores
+    p.off_red = align(a_bytes, 128);
+    p.off_recv = p.off_red + align(static_cast<int>(sizeof(float)) * p.warps_k * 8 * NB * p.red_pitch, 128);
+    const int ppr = 32 * p.warps_n;  // a power of two: warps_n is 1, 2, 4 or 8
     p.ppr_shift = 5;
     while ((1 << p.ppr_shift) < ppr) ++p.ppr_shift;
-    p.own_cols = (ppr + c.cluster_k - 1) / c.cluster_k;
+    p.own_items = (ppr / 2 + ck - 1) / ck;
+    p.own_cols = swiglu ? 2 * p.own_items : (ppr + ck - 1) / ck;
     p.own_magic = static_cast<uint32_t>(((1ull << 32) + p.own_cols - 1) / p.own_cols);
-    const size_t smem = static_cast<size_t>(p.off_recv) + 8 * (c.cluster_k * 8 * NB * p.own_cols) + 128;
+    p.item_magic = static_cast<uint32_t>(((1ull << 32) + p.own_items - 1) / p.own_items);
+    p.off_lora = p.off_recv + align(ck > 1 ? 8 * (ck * 8 * NB * p.own_cols) : 0, 128);
+    const size_t smem = static_cast<size_t>(p.off_lora) + lora_bytes + 128;
     if (smem > kMaxSmem) return KILN_W4A16_ERR_KERN_SHAPE;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(c.cluster_k, p.n / (kChunkCols * c.warps_n), (m + 8 * NB - 1) / (8 * NB));
-    cfg.blockDim = dim3(32 * c.warps_n * c.warps_k);
+    cfg.gridDim = dim3(ck, grid_y, (max_m + 8 * NB - 1) / (8 * NB));
+    cfg.blockDim = dim3(32 * p.warps_n * p.warps_k);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = c.cluster_k;
+    attrs[0].val.clusterDim.x = ck;
     attrs[0].val.clusterDim.y = 1;
     attrs[0].val.clusterDim.z = 1;
     attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -584,7 +708,7 @@ int launch_one(DecodeParams &p, const DecodeConfig &c, int m, cudaStream_t strea
     cfg.numAttrs = 2;
     if (cfg.gridDim.y > 65535 || cfg.gridDim.z > 65535) return KILN_W4A16_ERR_KERN_SHAPE;
     note_launch();
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_decode_kernel<NB>, p));
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_decode_kernel<NB, MULTI>, p));
 }
 
 }  // namespace
@@ -597,25 +721,68 @@ void decode_plan(int m, int n, int k, const DecodeOverride &ov, int out[4]) {
     out[3] = c.pass_groups;
 }
 
-int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
-    const DecodeConfig c = choose_config(a.m, a.n, a.k, ov);
+// One launch for `count` independent GEMMs.  The decomposition is the one the rule gives for a single GEMM with the
+// tallest m, the longest k and all the columns of the list side by side.
+int launch_decode_list(const DecodeItem *items, int count, cudaStream_t stream, const DecodeOverride &ov) {
+    if (count < 1 || count > kMaxProblems) return KILN_W4A16_ERR_ARG;
+    int max_m = 0, max_k = 0;
+    long long sum_n = 0;
+    for (int i = 0; i < count; ++i) {
+        max_m = std::max(max_m, items[i].m);
+        max_k = std::max(max_k, items[i].k);
+        sum_n += items[i].n;
+    }
+    if (sum_n > (1 << 30)) return KILN_W4A16_ERR_KERN_SHAPE;
+    const DecodeConfig c = choose_config(max_m, static_cast<int>(sum_n), max_k, ov);
     if (c.warps_n * c.warps_k > kMaxWarps[c.nb] || (c.warps_n & (c.warps_n - 1))) return KILN_W4A16_ERR_KERN_SHAPE;
     DecodeParams p{};
-    p.A = static_cast<const __nv_bfloat16 *>(a.A);
-    p.B = static_cast<const uint4 *>(a.B);
-    p.S = static_cast<const __half *>(a.S);
-    p.C = static_cast<__nv_bfloat16 *>(a.C);
-    p.m = a.m;
-    p.n = a.n;
-    p.k = a.k;
-    p.groups = a.k / kGroup;
-    p.groups_per_cta = c.groups_per_cta;
-    p.pass_groups = c.pass_groups;
+    p.count = count;
     p.warps_n = c.warps_n;
     p.warps_k = c.warps_k;
-    p.per_column = a.groupsize == -1;
-    if (c.nb == 1) return launch_one<1>(p, c, a.m, a.stream);
-    return launch_one<2>(p, c, a.m, a.stream);
+    for (int i = 0; i < count; ++i) {
+        const DecodeItem &it = items[i];
+        DecodeProblem &q = p.prob[i];
+        if (it.n % (kChunkCols * c.warps_n) != 0) return KILN_W4A16_ERR_KERN_SHAPE;
+        if (it.lora_r < 0 || it.lora_r > 128 || it.lora_r % 8 != 0) return KILN_W4A16_ERR_ARG;
+        q.A = static_cast<const __nv_bfloat16 *>(it.A);
+        q.B = static_cast<const uint4 *>(it.B);
+        q.S = static_cast<const __half *>(it.S);
+        q.C = static_cast<__nv_bfloat16 *>(it.C);
+        q.lora_t = it.lora_r ? static_cast<const float *>(it.lora_t) : nullptr;
+        q.lora_b = static_cast<const __nv_bfloat16 *>(it.lora_b);
+        q.lora_r = it.lora_r;
+        q.swiglu = it.swiglu;
+        q.m = it.m;
+        q.n = it.n;
+        q.k = it.k;
+        q.groups = it.k / kGroup;
+        q.groups_per_cta = ceil_div(q.groups, c.cluster_k);
+        const int rows = it.m < 8 * c.nb ? it.m : 8 * c.nb;
+        int pg = (kStageBytes / rows - 16) / 256;
+        if (pg < 1) pg = 1;
+        q.pass_groups = q.groups_per_cta < pg ? q.groups_per_cta : pg;
+        q.per_column = it.groupsize == -1;
+    }
+    if (c.nb == 1)
+        return count == 1 ? launch_list<1, false>(p, c.cluster_k, max_m, stream) : launch_list<1, true>(p, c.cluster_k, max_m, stream);
+    return count == 1 ? launch_list<2, false>(p, c.cluster_k, max_m, stream) : launch_list<2, true>(p, c.cluster_k, max_m, stream);
+}
+
+int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
+    DecodeItem it{};
+    it.A = a.A;
+    it.B = a.B;
+    it.S = a.S;
+    it.C = a.C;
+    it.m = a.m;
+    it.n = a.n;
+    it.k = a.k;
+    it.groupsize = a.groupsize;
+    it.lora_t = a.lora_t;
+    it.lora_b = a.lora_b;
+    it.lora_r = a.lora_r;
+    it.swiglu = a.swiglu;
+    return launch_decode_list(&it, 1, a.stream, ov);
 }
 
 }  // namespace kiln

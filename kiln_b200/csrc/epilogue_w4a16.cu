@@ -1,0 +1,96 @@
+// Small kernels around the W4A16 GEMM's epilogue options.
+//
+//  * lora_down_kernel: t = scale * x * A^T, the rank-r projection of kiln's LoRA delta
+//    (kiln-model/src/lora_loader.rs:213-233: delta = x @ A^T @ B^T * scale).  The GEMM kernel then adds t * B^T to its
+//    fp32 sums before rounding, so the delta never exists as a matrix of its own.
+//  * finish_kernel: for batch sizes beyond the decode kernel's range, where the options are not fused yet:
+//    C = epilogue(base), base being the bf16 GEMM result in the workspace (LoRA delta added, SwiGLU applied).
+#include "w4a16_common.cuh"
+
+namespace kiln {
+namespace {
+
+// grid = (ceil(r / 8), m), block = 256: warp w of a CTA computes t[row][8 * blockIdx.x + w].
+__global__ void __launch_bounds__(256) lora_down_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
+                                                        float scale, int k, int r, float *__restrict__ t) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.y, j = blockIdx.x * 8 + warp;
+    pdl_wait();  // x may be the previous kernel's output; t may still be read by it
+    if (j >= r) return;
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(row) * k);
+    const uint4 *ar = reinterpret_cast<const uint4 *>(a + static_cast<size_t>(j) * k);
+    float sum = 0.f;
+    for (int i = lane; i < k / 8; i += 32) {
+        const uint4 xv = ld_cg_v4(xr + i), av = ar[i];
+        const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, as[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            sum += __uint_as_float(xs[e] << 16) * __uint_as_float(as[e] << 16) +
+                   __uint_as_float(xs[e] & 0xFFFF0000u) * __uint_as_float(as[e] & 0xFFFF0000u);
+    }
+#pragma unroll
+    for (int sh = 16; sh >= 1; sh >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sh);
+    if (lane == 0) t[static_cast<size_t>(row) * r + j] = sum * scale;
+}
+
+__device__ __forceinline__ float lora_dot(const float *t, const __nv_bfloat16 *b, int r) {
+    float d = 0.f;
+    for (int j = 0; j < r; j += 2) {
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(b + j);
+        d += t[j] * __uint_as_float(w << 16) + t[j + 1] * __uint_as_float(w & 0xFFFF0000u);
+    }
+    return d;
+}
+
+// One thread per output element of C ([m, n], or [m, n/2] with SwiGLU).
+__global__ void __launch_bounds__(256) finish_kernel(const __nv_bfloat16 *__restrict__ base, __nv_bfloat16 *__restrict__ c, int m,
+                                                     int n, const float *__restrict__ t, const __nv_bfloat16 *__restrict__ lb, int r,
+                                                     int swiglu) {
+    const int n_out = swiglu ? n / 2 : n;
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<size_t>(m) * n_out) return;
+    const int row = static_cast<int>(idx / n_out), oc = static_cast<int>(idx - static_cast<size_t>(row) * n_out);
+    auto value = [&](int col) {
+        float v = __bfloat162float(base[static_cast<size_t>(row) * n + col]);
+        if (r) v += lora_dot(t + static_cast<size_t>(row) * r, lb + static_cast<size_t>(col) * r, r);
+        return v;
+    };
+    if (!swiglu) {
+        c[idx] = __float2bfloat16(value(oc));
+    } else {
+        const int cg = (oc >> 5) * 64 + (oc & 31);  // gate column; its up column is 32 further
+        const float g = value(cg), u = value(cg + 32);
+        c[idx] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+    }
+}
+
+}  // namespace
+
+int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, float *t, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((r + 7) / 8, m, 1);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (m > 65535) return KILN_W4A16_ERR_KERN_SHAPE;
+    note_launch();
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, lora_down_kernel, static_cast<const __nv_bfloat16 *>(x),
+                                                static_cast<const __nv_bfloat16 *>(lora_a), scale, k, r, t));
+}
+
+int launch_finish(const void *base, void *c, int m, int n, const float *t, const void *lora_b, int r, int swiglu,
+                  cudaStream_t stream) {
+    const size_t total = static_cast<size_t>(m) * (swiglu ? n / 2 : n);
+    const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    note_launch();
+    finish_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(base), static_cast<__nv_bfloat16 *>(c), m, n, t,
+                                              static_cast<const __nv_bfloat16 *>(lora_b), r, swiglu);
+    return record_cuda_error(cudaGetLastError());
+}
+
+}  // namespace kiln

@@ -55,6 +55,8 @@ struct PrefillParams {
     int sk_first_tile;  // stream-K: tiles below this index are dealt whole (a multiple of the grid size)
     int sk_ctas;        // stream-K: CTAs that share the remaining tiles (<= grid size)
     int tile_elems;   // rows * columns of one output tile (stream-K slabs are tile-shaped)
+    unsigned long long wait_limit_ns;  // every bounded wait of the launch gives up after this long
+    int test_drop_a_load;  // test hook: the activation tile of this K-step (counted per CTA) is announced but never copied; -1 = off
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -266,9 +268,10 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 for (int ki = ki0; ki < ki1; ++ki, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x100u | s))) break;
+                    if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x100u | s, p.wait_limit_ns))) break;
                     mbar_arrive_expect_tx(full_a(s), C::kABytes);
-                    tma_load_2d(smem_base + s * C::kStageBytes, &tmap_a, ki * BK, mt * (BM * MT), full_a(s));
+                    if (static_cast<int>(it) != p.test_drop_a_load)
+                        tma_load_2d(smem_base + s * C::kStageBytes, &tmap_a, ki * BK, mt * (BM * MT), full_a(s));
                 }
             }
             if (!ok) {
@@ -298,13 +301,13 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 for (int ki = ki0; ki < ki1; ++ki, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s))) break;
+                    if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s, p.wait_limit_ns))) break;
                     tc_fence_after();
                     const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes);
                     for (int h = h0; h < h1; ++h) {
                         const uint32_t acc = acc0 + h;
                         if (ki == ki0) {  // first write into this accumulator: the epilogue must have drained it
-                            if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc))) break;
+                            if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc, p.wait_limit_ns))) break;
                             tc_fence_after();
                         }
                         const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes + h * (BM * BK * 2));
@@ -331,7 +334,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll 1
             for (int h = 0; h < MT && ok; ++h) {
             const uint32_t acc = acc0 + h;
-            if (!(ok = mbar_wait(tmem_full(acc), acc_ph, abort_flag, p.status, 0x500u | acc))) break;
+            if (!(ok = mbar_wait(tmem_full(acc), acc_ph, abort_flag, p.status, 0x500u | acc, p.wait_limit_ns))) break;
             tc_fence_after();
             const int row = (mt * MT + h) * BM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
@@ -528,7 +531,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         }
                     }
                 }
-                if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x600u | s))) break;
+                if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x600u | s, p.wait_limit_ns))) break;
                 const uint32_t b_tile = smem_base + s * C::kStageBytes + C::kABytes;
 #pragma unroll
                 for (int b = 0; b < C::kBlocksPerWarp; ++b) {
@@ -712,8 +715,11 @@ StreamKPlan streamk_plan(int tiles, int k_iters, int grid) {
 }
 
 PrefillConfig g_prefill_override{0, 0, 0, 0};
+unsigned long long g_wait_limit_ns = kWaitLimitNs;
+int g_test_drop_a_load = -1;
 
-PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool allow_scratch = true) {
+PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool allow_scratch = true,
+                             size_t max_split_bytes = ~static_cast<size_t>(0)) {
     const int sms = device_sm_count();
     const int k_iters = k / BK;
     {  // tuning hook (kiln_w4a16_set_prefill_override): taken when it is legal for this problem, else the rule below
@@ -721,6 +727,7 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool 
         const bool legal = (o.bn == 128 || o.bn == 256) && n % o.bn == 0 && (o.mt == 1 || (o.mt == 2 && allow_pairs && m > BM)) &&
                            o.splits >= 1 && o.splits <= 8 && k_iters / o.splits >= 1 && (o.stream_k == 0 || o.stream_k == 1) &&
                            !(o.stream_k && o.splits != 1) && (allow_scratch || (o.splits == 1 && !o.stream_k));
+        // (a forced split larger than max_split_bytes is returned as it is: the no-allocation entry then refuses the call)
         if (legal) return o;
     }
     PrefillConfig best{256, 1, 1, 0};
@@ -733,6 +740,7 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool 
                 const int bn = bns[bi], s = ss[si];
                 if (k_iters / s < 8) continue;
                 if (s > 1 && !allow_scratch) continue;
+                if (s > 1 && static_cast<size_t>(s) * m * n * sizeof(float) > max_split_bytes) continue;
                 if (mt == 2 && m <= BM) continue;
                 const int m_tiles = (m + BM * mt - 1) / (BM * mt);
                 const long long units = static_cast<long long>(m_tiles) * (n / bn) * s;
@@ -841,6 +849,9 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillP
 
 }  // namespace
 
+void set_wait_limit_ns(unsigned long long ns) { g_wait_limit_ns = ns ? ns : kWaitLimitNs; }
+void set_test_drop_a_load(int k_step) { g_test_drop_a_load = k_step; }
+
 void set_prefill_override(int bn, int splits, int mt, int stream_k) {
     g_prefill_override = PrefillConfig{bn, splits, mt, stream_k};
 }
@@ -871,7 +882,7 @@ int launch_prefill(const GemmArgs &a) {
     uint32_t *status = device_status_word();
     if (!status) return KILN_W4A16_ERR_CUDA;
     const bool fused = a.n_peers > 0 || a.mc_c;  // the peer-store epilogue needs whole tiles: no split-K, no stream-K
-    const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused);
+    const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused && !a.no_scratch);
 
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
@@ -905,6 +916,8 @@ int launch_prefill(const GemmArgs &a) {
     p.mc_c = static_cast<__nv_bfloat16 *>(a.mc_c);
     for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;
+    p.wait_limit_ns = g_wait_limit_ns;
+    p.test_drop_a_load = g_test_drop_a_load;
     p.tile_elems = BM * c.mt * c.bn;
     const StreamKPlan plan = streamk_plan(p.m_tiles * p.n_tiles, p.k_iters, device_sm_count());
     p.sk_first_tile = plan.first_tile;
@@ -980,8 +993,39 @@ int static_state(StaticDeviceState **out) {
     return 0;
 }
 
+PrefillConfig noalloc_config(int m, int n, int k) {
+    return choose_prefill(m, n, k, /*allow_pairs=*/false, /*allow_scratch=*/true, KILN_W4A16_NOALLOC_SCRATCH_BYTES);
+}
+
 }  // namespace
+
+// Reads and clears the status word of the no-allocation entry's launches on the current device (0 if that entry has
+// never run there).  No allocation: the word lives in the library image.
+int static_status_read_clear(cudaStream_t st, uint32_t *out) {
+    *out = 0;
+    int dev = 0;
+    if (int rc = record_cuda_error(cudaGetDevice(&dev))) return rc;
+    if (dev < 0 || dev >= 64) return 0;
+    StaticDeviceState *state = nullptr;
+    if (int rc = static_state(&state)) return rc;
+    if (int rc = record_cuda_error(cudaMemcpyAsync(out, state->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, st))) return rc;
+    if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
+    if (*out != 0) {
+        if (int rc = record_cuda_error(cudaMemsetAsync(state->status, 0, sizeof(uint32_t), st))) return rc;
+        if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
+    }
+    return 0;
+}
 }  // namespace kiln
+
+extern "C" void kiln_w4a16_noalloc_plan(int m, int n, int k, int out[4]) {
+    if (!out || m <= 0 || n <= 0 || k <= 0) return;
+    const kiln::PrefillConfig c = kiln::noalloc_config(m, n, k);
+    out[0] = c.bn;
+    out[1] = c.splits;
+    out[2] = c.mt;
+    out[3] = c.stream_k;
+}
 
 extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const void *B, void *C, const void *s,
                                                             int m, int n, int k, int groupsize, void *stream) {
@@ -995,7 +1039,9 @@ extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const
         return KILN_W4A16_ERR_ALIGNMENT;
     if (!prefill_supported(m, n, k, groupsize)) return KILN_W4A16_ERR_KERN_SHAPE;
 
-    const PrefillConfig c = choose_prefill(m, n, k, /*allow_pairs=*/false);
+    // the best tiling whose split-K slabs fit the array (a tiling without a split always does); only a tiling forced
+    // through the tuning hook can still ask for more
+    const PrefillConfig c = noalloc_config(m, n, k);
     const size_t need = c.splits > 1 ? static_cast<size_t>(c.splits) * m * n * sizeof(float) : 0;
     if (need > KILN_W4A16_NOALLOC_SCRATCH_BYTES) return KILN_W4A16_ERR_STATIC_SCRATCH;
 
@@ -1030,6 +1076,8 @@ extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const
     p.splits = c.splits;
     p.k_iters = k / BK;
     p.per_column = groupsize == -1;
+    p.wait_limit_ns = g_wait_limit_ns;
+    p.test_drop_a_load = -1;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     CUtensorMap tmap_c;
     if (!encode_c_map(enc, &tmap_c, C, m, n)) return KILN_W4A16_ERR_CUDA;

@@ -354,6 +354,12 @@ __global__ void permute_scales_kernel(const uint16_t *scales, int n, int per_col
     out[static_cast<size_t>(grp) * n + pos] = scales[static_cast<size_t>(grp) * n + col];
 }
 
+// The GEMM kernels are launched with programmatic stream serialisation and read the packed weights and scales BEFORE
+// their grid-dependency wait (weights normally never depend on the kernel before a GEMM).  A GEMM enqueued right after a
+// device pack would break that assumption, so every device pack entry point ends with this ordinary launch: it starts
+// only when the pack kernels have completed and flushed, and it is what the next kernel's early part overlaps with.
+__global__ void pack_fence_kernel() {}
+
 }  // namespace
 }  // namespace kiln
 
@@ -377,7 +383,8 @@ kiln_w4a16_status_t kiln_w4a16_quantize_and_pack_device(const void *weight, int 
         pack_scales_kernel<false><<<g1, 128, 0, st>>>(weight, n, g, groupsize == -1, scales_f16, scales_nat);
         pack_words_kernel<false><<<g2, 128, 0, st>>>(weight, n, g, scales_nat, b_packed, dequant);
     }
-    note_launch(2);
+    pack_fence_kernel<<<1, 32, 0, st>>>();
+    note_launch(3);
     int rc = record_cuda_error(cudaGetLastError());
     const int rc2 = record_cuda_error(cudaFreeAsync(scales_nat, st));
     return rc ? rc : rc2;
@@ -395,7 +402,8 @@ kiln_w4a16_status_t kiln_w4a16_repack_device(const uint8_t *q, const uint16_t *s
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     repack_words_kernel<<<dim3(n / 64, k / 16), 128, 0, st>>>(q, n, b_packed);
     permute_scales_kernel<<<dim3((n + 127) / 128, k / g), 128, 0, st>>>(scales, n, groupsize == -1, scales_perm);
-    note_launch(2);
+    pack_fence_kernel<<<1, 32, 0, st>>>();
+    note_launch(3);
     return record_cuda_error(cudaGetLastError());
 }
 
@@ -411,7 +419,7 @@ kiln_w4a16_status_t kiln_w4a16_repack_gptq_device(const int32_t *qweight, const 
     if (g <= 0 || k % g != 0) return KILN_W4A16_ERR_PROB_SHAPE;
     if (!qweight || !qzeros || !scales || !b_packed || !scales_perm) return KILN_W4A16_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    unsigned launches = 2;
+    unsigned launches = 3;
     if (asymmetric) {
         if (int rc = record_cuda_error(cudaMemsetAsync(asymmetric, 0, sizeof(uint32_t), st))) return rc;
         const size_t words = static_cast<size_t>(k / g) * (n / 8);
@@ -421,6 +429,7 @@ kiln_w4a16_status_t kiln_w4a16_repack_gptq_device(const int32_t *qweight, const 
     }
     repack_gptq_words_kernel<<<dim3(n / 64, k / 16), 128, 0, st>>>(qweight, n, b_packed);
     permute_scales_kernel<<<dim3((n + 127) / 128, k / g), 128, 0, st>>>(scales, n, groupsize == -1, scales_perm);
+    pack_fence_kernel<<<1, 32, 0, st>>>();
     note_launch(launches);
     return record_cuda_error(cudaGetLastError());
 }

@@ -7,8 +7,8 @@
 
 namespace kiln {
 
-// A wait gives up after this much wall-clock time (nanoseconds of %globaltimer).  Legitimate
-// waits in these kernels last microseconds to a few milliseconds.
+// A wait gives up after this much wall-clock time (nanoseconds of %globaltimer) unless the launch says otherwise.
+// Legitimate waits in these kernels last microseconds to a few milliseconds.
 constexpr unsigned long long kWaitLimitNs = 400ull * 1000 * 1000;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -43,14 +43,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 // Bounded wait.  Returns false if the CTA is aborting (this wait or another one ran out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code) {
+                                          uint32_t *status, uint32_t code, unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 15) == 15) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitLimitNs) break;
+            if (global_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;

@@ -126,6 +126,22 @@ struct GemmArgs {
     int n_peers = 0, ldc = 0, col0 = 0;
     // the same with one NVSwitch multicast address for the whole group instead of per-GPU pointers (multimem.st)
     void *mc_c = nullptr;
+    // epilogue options (decode kernel): LoRA delta C += lora_t * lora_b^T with lora_t fp32 [m, lora_r] = scale * x * A^T
+    // and lora_b bf16 [n, lora_r]; swiglu: columns are gate/up interleaved in runs of 32, C is [m, n/2]
+    bool no_scratch = false;  // the tcgen05 kernel may not use the workspace (legacy entry point: its caller's buffer is tiny)
+    const void *lora_t = nullptr;
+    const void *lora_b = nullptr;
+    int lora_r = 0;
+    int swiglu = 0;
+};
+
+// One GEMM of a grouped decode launch.
+struct DecodeItem {
+    const void *A, *B, *S;
+    void *C;
+    int m, n, k, groupsize;
+    const void *lora_t, *lora_b;
+    int lora_r, swiglu;
 };
 
 struct DecodeOverride {
@@ -139,10 +155,16 @@ uint32_t *device_status_word();        // per-device word written by bounded wai
 
 int launch_decode(const GemmArgs &a, const DecodeOverride &ov);
 void decode_plan(int m, int n, int k, const DecodeOverride &ov, int out[4]);
+int launch_decode_list(const DecodeItem *items, int count, cudaStream_t stream, const DecodeOverride &ov);
+int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, float *t, cudaStream_t stream);
+int launch_finish(const void *base, void *c, int m, int n, const float *t, const void *lora_b, int r, int swiglu, cudaStream_t stream);
 int launch_prefill(const GemmArgs &a);
 size_t prefill_workspace_bytes(int m, int n, int k);
 void set_prefill_override(int bn, int splits, int mt, int stream_k);
+void set_wait_limit_ns(unsigned long long ns);
+void set_test_drop_a_load(int k_step);
 void prefill_plan(int m, int n, int k, int out[4]);
 bool prefill_supported(int m, int n, int k, int groupsize);
+int static_status_read_clear(cudaStream_t st, uint32_t *out);
 
 }  // namespace kiln

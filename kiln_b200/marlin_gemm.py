@@ -11,6 +11,7 @@ class KilnMarlinError(RuntimeError):
 
 
 _workspaces: dict = {}
+_retired: list = []
 
 
 def workspace_bytes(m: int, n: int, k: int) -> int:
@@ -18,12 +19,16 @@ def workspace_bytes(m: int, n: int, k: int) -> int:
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Per-device scratch that only grows; replaces the reference's per-call
-    `Tensor::zeros` workspace (lib.rs:176-178)."""
-    ws = _workspaces.get(device)
+    """Scratch that only grows, one buffer per (device, stream): GEMMs on different streams may overlap on the GPU and
+    must not share split-K partial sums.  Replaces the reference's per-call `Tensor::zeros` workspace (lib.rs:176-178).
+    A buffer that is outgrown is kept alive until the process ends (a kernel of an earlier call may still use it)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired.append(ws)
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[device] = ws
+        _workspaces[key] = ws
     return ws
 
 

@@ -23,6 +23,7 @@ fn main() {
     for f in [
         "api.cu",
         "decode_w4a16.cu",
+        "epilogue_w4a16.cu",
         "prefill_w4a16_umma.cu",
         "repack.cu",
     ] {

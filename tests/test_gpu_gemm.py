@@ -162,6 +162,47 @@ def test_legacy_symbol_and_stream(cuda_device):
     assert lib.kiln_w4a16_check_device_status(None, None) == 0
 
 
+def test_legacy_symbol_never_touches_the_references_small_workspace(cuda_device):
+    """An unmodified reference wrapper passes its (n / 128) * 16 int32 lock array (kiln-marlin-gemm/src/lib.rs:174-178).
+    At a batch size where the regular entry point would split K into a caller-sized workspace, the legacy symbol must
+    leave that small buffer, and what surrounds it, alone."""
+    lib = _lib.lib()
+    m, k, n = 256, 9216, 2560
+    assert lib.kiln_w4a16_workspace_bytes(m, n, k) > (n // 128) * 16 * 4, "the regular entry point would use scratch here"
+    case = make_case(8, k, n, seed=77, device=cuda_device)
+    a = torch.cat([case["a_t"]] * (m // 8), dim=0).contiguous()
+    words = (n // 128) * 16
+    buf = torch.full((words + 2048,), 0x5A5A5A5A, dtype=torch.int32, device=cuda_device)
+    ws = buf[1024:1024 + words]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=cuda_device)
+    rc = lib.kiln_marlin_w4a16_gemm(a.data_ptr(), case["b_t"].data_ptr(), out.data_ptr(), case["s_t"].data_ptr(), m, n, k,
+                                    ws.data_ptr(), 128, 0, torch.cuda.current_stream().cuda_stream, -1, -1, -1, 16)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert (buf == 0x5A5A5A5A).all(), "the legacy entry point wrote into or around the reference-sized workspace"
+    assert rel_err(from_torch_bf16(out[:8]), case["ref"]) <= REL_TOL
+    assert torch.equal(out[:8], out[m - 8:])
+
+
+def test_gemm_right_after_a_device_pack_on_the_same_stream(cuda_device):
+    """The GEMM kernels read weights before their grid-dependency wait; the device pack entry points end with an
+    ordinary launch so that a GEMM enqueued right behind a pack still sees the packed weights."""
+    k, n, m = 2560, 4096, 4
+    g = torch.Generator(device=cuda_device)
+    g.manual_seed(3)
+    a_t = torch.randn((m, k), device=cuda_device, generator=g).to(torch.bfloat16)
+    for i in range(4):  # a fresh weight each time: the packed tensors of the previous round must not be what is read
+        w = (torch.randn((k, n), device=cuda_device, generator=g) * 0.02).to(torch.bfloat16)
+        proj = kiln_b200.pack_from_bf16(w)
+        out = kiln_b200.matmul_bf16(a_t, proj)  # no synchronisation between the pack and the GEMM
+        ref = a_t.float() @ w.float()
+        torch.cuda.synchronize()
+        assert float((out.float() - ref).abs().max() / ref.abs().max()) < 0.2  # int4 quantisation error, not garbage
+        again = kiln_b200.matmul_bf16(a_t, proj)
+        torch.cuda.synchronize()
+        assert torch.equal(out, again), "the GEMM right behind the pack read something else than the packed weights"
+
+
 def test_rank3_activation_through_marlin_proj(cuda_device):
     """matmul_bf16 flattens [b, s, k] like kiln-model/src/marlin_proj.rs:285-319."""
     case = make_case(6, 256, 512, seed=21, device=cuda_device)

@@ -115,4 +115,10 @@ def test_packed_cache_round_trip(cuda_device, tmp_path):
     third = cache.get_or_pack("layers.0.mlp.gate", w2)
     assert torch.equal(third.b_packed, kiln_b200.pack_from_bf16(w2).b_packed)
     assert len(list(tmp_path.iterdir())) == 1
+    # two rows swapped: same multiset of words, different weight -> repacked as well
+    w3 = w2.clone()
+    w3[[1, 2]] = w3[[2, 1]]
+    fourth = cache.get_or_pack("layers.0.mlp.gate", w3)
+    assert torch.equal(fourth.b_packed, kiln_b200.pack_from_bf16(w3).b_packed)
+    assert not torch.equal(fourth.b_packed, third.b_packed)
     assert cache.get_or_pack("odd", torch.zeros((100, 256), device=cuda_device, dtype=torch.bfloat16)) is None

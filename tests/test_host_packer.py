@@ -132,3 +132,29 @@ def test_gptq_repack_is_exact_for_symmetric_checkpoints_and_refused_otherwise():
     qw, qz = oracle.np_gptq_pack(q, zeros)
     with pytest.raises(ValueError, match="2 zero-points"):
         pack.repack_gptq(qw, qz, s, g)
+
+
+@pytest.mark.parametrize("gs", [128, -1])
+def test_interleave_gate_up_is_the_packed_interleaved_matrix(gs):
+    """Fusing packed gate and up projections by shuffling words gives bit for bit what packing the matrix with its
+    columns interleaved in runs of 32 gives."""
+    import torch
+
+    import kiln_b200
+
+    k, n = 256, 256
+    rng = np.random.default_rng(1)
+    qg, qu = rng.integers(0, 16, (k, n), dtype=np.uint8), rng.integers(0, 16, (k, n), dtype=np.uint8)
+    ng = k // 128 if gs == 128 else 1
+    sg, su = rng.random((ng, n)).astype(np.float16), rng.random((ng, n)).astype(np.float16)
+
+    def proj(q, s):
+        return kiln_b200.MarlinPackedProj(torch.from_numpy(C.pack_nibbles(q)),
+                                          torch.from_numpy(C.permute_scales(s, gs).view(np.int16).copy()).view(torch.float16), gs, k, n)
+
+    f = kiln_b200.interleave_gate_up(proj(qg, sg), proj(qu, su))
+    qi = np.stack([qg.reshape(k, n // 32, 32), qu.reshape(k, n // 32, 32)], axis=2).reshape(k, 2 * n)
+    si = np.stack([sg.reshape(ng, n // 32, 32), su.reshape(ng, n // 32, 32)], axis=2).reshape(ng, 2 * n)
+    assert (f.b_packed.numpy() == C.pack_nibbles(qi)).all()
+    assert (f.scales.view(torch.int16).numpy().view(np.uint16) == C.permute_scales(si, gs).view(np.uint16)).all()
+    assert f.n == 2 * n and f.k == k

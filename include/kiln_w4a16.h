@@ -231,7 +231,7 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
 void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]);
 
 /* Tuning hook: the M at and above which the tcgen05 prefill kernel is used.  <= 0 restores the
- * built-in rule (M >= 17 for weights of 16 M elements and more, M >= 33 or 49 for smaller ones, M > 256 for
+ * built-in rule (M >= 33, or 49 for projections narrower than 4096 columns with fewer than 16 M weights, M > 256 for
  * projections of at most 1024 columns); a huge value disables that kernel, 1 forces it. */
 void kiln_w4a16_set_prefill_min_m(int min_m);
 

@@ -73,18 +73,20 @@ static int validate(const GemmArgs &a) {
 }
 
 // Kernel choice (measured on B200, CUDA-graph replay over rotating weights).  The decode kernel handles 8 or 16 rows per
-// block of CTAs and repeats the int4 dequant for every block; the tcgen05 kernel dequantises once per 128 rows but works
-// in 128-column tiles.  Crossovers: weights of 16 M elements and more (gate+up, down, GDN-in): tcgen05 from M = 17;
-// smaller ones (q, o, GDN-out): from M = 33 when N >= 4096, else from M = 49; projections of 1024 columns or fewer (k, v: four
-// to eight tiles for 148 SMs) stay on the decode kernel up to M = 256 (k at M=256: 9.4 vs 19.6 us).
+// block of CTAs and repeats the int4 dequant for every block; the tcgen05 kernel dequantises once per 128 rows but pays
+// a fixed cost per 64-K step of a tile.  Measured crossovers: up to 32 rows (two blocks of 16) the decode kernel wins on
+// every shape (gate+up M=32: 19.2 vs 23.1 us, q: 8.3 vs 10.1); a third block costs it more than the tcgen05 kernel's
+// tile (gate+up M=48: 32.4 vs 23.2 us, q: 12.7 vs 10.7), except on projections of about 2560 columns, which have few
+// tiles for 148 SMs (o M=48: 10.0 vs 11.3 us, M=64: 14.4 vs 12.3) and switch at 49, and on projections of 1024 columns
+// or fewer (k, v: four to eight tiles), which stay on the decode kernel up to M = 256 (k at M=128: 6.4 vs 16.1 us).
 // kiln_w4a16_set_prefill_min_m replaces the rule by a plain threshold.
 static bool use_prefill(int m, int n, int k, int groupsize) {
     if (!prefill_supported(m, n, k, groupsize)) return false;
     const int min_m = g_prefill_min_m.load(std::memory_order_relaxed);
     if (min_m != kDefaultPrefillMinM) return m >= min_m;
     if (n <= 1024) return m > 256;
-    if (static_cast<long long>(n) * k >= (16LL << 20)) return m >= 17;
-    return m >= (n >= 4096 ? 33 : 49);
+    if (n >= 4096 || static_cast<long long>(n) * k >= (16LL << 20)) return m >= 33;
+    return m >= 49;
 }
 
 static int gemm(const GemmArgs &a) {

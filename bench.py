@@ -35,7 +35,7 @@ DECODE_MS = (1, 4, 8, 16)
 PREFILL = [(m, s) for s in ("gate_up", "down") for m in (512, 2048, 8192)]
 ROT = 8  # distinct weight copies per shape
 SEED = 1234
-NCU_TRAFFIC_RATIO = 24.371456 / 24.372224  # dram__bytes_read+write of the captured launch / its algorithmic bytes
+NCU_TRAFFIC_RATIO = 24.375040 / 24.372224  # dram__bytes_read+write of the captured launch / its algorithmic bytes
 L2_BYTES = 126e6
 
 
@@ -813,7 +813,7 @@ def run_ours(args):
             "frac": value / world / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (MEASURED_PEAKS.json hbm_gbs, copy)",
             "kernel": "w4a16_decode_kernel",
             # DRAM bytes per (average) launch: the ncu capture of one launch (gate+up, M=1: profiles/decode_kernel_gate_up_m1.txt)
-            # read 24.371 MB and wrote 0 against 24.372 MB algorithmic, i.e. every weight byte crosses DRAM exactly once;
+            # read 24.375 MB and wrote 0 against 24.372 MB algorithmic, i.e. every weight byte crosses DRAM exactly once;
             # the figure here scales that ratio to the sweep's average launch
             "traffic": NCU_TRAFFIC_RATIO * step_bytes / launches_per_step,
             "traffic_source": "ncu capture of gate_up M=1 (dram read+write / algorithmic = %.4f), scaled by bytes" % NCU_TRAFFIC_RATIO,

@@ -5,7 +5,10 @@
 //! validates shapes the way the original wrapper does, borrows device pointers from candle
 //! and forwards them.  Differences from the original wrapper are all removals: no bf16<->fp16
 //! casts (the kernels read and write bf16), no zeroed lock buffer per call (split-K scratch is
-//! a cached per-device buffer, and the decode path needs none), no hard-coded device 0.
+//! a per-device buffer that is created once, grows when a larger problem needs it and is never
+//! cleared; batch sizes below 33 need none), no hard-coded device 0.  The output tensor is still
+//! created with `Tensor::zeros`, as in the original: candle offers no safe uninitialised
+//! constructor, and the kernels overwrite every element.
 //!
 //! NOTE: authored without a Rust toolchain at hand; it has not been compiled.
 
@@ -14,6 +17,23 @@ use candle_core::{
 };
 use half::f16;
 use std::ffi::c_void;
+use std::sync::Mutex;
+
+/// Split-K scratch, one buffer per CUDA device ordinal, kept for the life of the process.  The kernels
+/// neither expect it to be zero nor leave anything in it that a later call reads.  Calls on one device
+/// are expected on one stream (candle's), as in the original wrapper.
+static WORKSPACES: Mutex<Vec<(usize, Tensor)>> = Mutex::new(Vec::new());
+
+fn workspace_for(device: &candle_core::Device, ordinal: usize, bytes: usize) -> Result<Tensor> {
+    let mut all = WORKSPACES.lock().unwrap();
+    if let Some((_, t)) = all.iter().find(|(o, t)| *o == ordinal && t.elem_count() >= bytes) {
+        return Ok(t.clone());
+    }
+    let t = Tensor::zeros((bytes.max(1 << 20),), DType::U8, device)?;
+    all.retain(|(o, _)| *o != ordinal);
+    all.push((ordinal, t.clone()));
+    Ok(t)
+}
 
 unsafe extern "C" {
     fn kiln_w4a16_gemm_bf16(
@@ -69,6 +89,30 @@ unsafe extern "C" {
         asymmetric: *mut u32,
         stream: *mut c_void,
     ) -> i32;
+    /// the GEMM with epilogue options: LoRA delta and / or SwiGLU of an interleaved gate+up matrix
+    pub fn kiln_w4a16_gemm_bf16_ex(
+        a: *const c_void,
+        b: *const c_void,
+        c: *mut c_void,
+        s: *const c_void,
+        m: i32,
+        n: i32,
+        k: i32,
+        groupsize: i32,
+        epilogue: *const KilnW4a16Epilogue,
+        workspace: *mut c_void,
+        workspace_bytes: usize,
+        stream: *mut c_void,
+    ) -> i32;
+    pub fn kiln_w4a16_workspace_bytes_ex(m: i32, n: i32, k: i32, epilogue: *const KilnW4a16Epilogue) -> usize;
+    /// several independent GEMMs (q, k, v of a layer) in one launch at decode batch sizes
+    pub fn kiln_w4a16_gemm_bf16_grouped(
+        problems: *const KilnW4a16Problem,
+        count: i32,
+        workspace: *mut c_void,
+        workspace_bytes: usize,
+        stream: *mut c_void,
+    ) -> i32;
     /// column-parallel GEMM whose epilogue stores into every GPU's `[m, ldc]` buffer
     pub fn kiln_w4a16_gemm_bf16_allgather(
         a: *const c_void,
@@ -84,6 +128,29 @@ unsafe extern "C" {
         col0: i32,
         stream: *mut c_void,
     ) -> i32;
+}
+
+/// `kiln_w4a16_epilogue_t` of include/kiln_w4a16.h.
+#[repr(C)]
+pub struct KilnW4a16Epilogue {
+    pub swiglu: i32,
+    pub lora_a: *const c_void,
+    pub lora_b: *const c_void,
+    pub lora_rank: i32,
+    pub lora_scale: f32,
+}
+
+/// `kiln_w4a16_problem_t` of include/kiln_w4a16.h.
+#[repr(C)]
+pub struct KilnW4a16Problem {
+    pub a: *const c_void,
+    pub b: *const c_void,
+    pub c: *mut c_void,
+    pub s: *const c_void,
+    pub m: i32,
+    pub n: i32,
+    pub k: i32,
+    pub groupsize: i32,
 }
 
 /// `a [m,k] bf16` x `b_packed [k/16, n*16/8] i32` x `scales [k/groupsize, n] f16` -> `[m,n] bf16`.
@@ -144,7 +211,11 @@ pub fn marlin_w4a16_gemm(
     // fully overwritten by the kernel; zeros() only because candle has no uninitialised constructor here
     let c = Tensor::zeros((m, n), DType::BF16, device)?;
     let ws_bytes = unsafe { kiln_w4a16_workspace_bytes(m as i32, n as i32, k as i32) };
-    let ws = Tensor::zeros((ws_bytes.max(16),), DType::U8, device)?;
+    let ordinal = match device {
+        candle_core::Device::Cuda(d) => d.ordinal(),
+        _ => 0,
+    };
+    let ws = workspace_for(device, ordinal, ws_bytes.max(16))?;
 
     {
         let (a_st, a_l) = a.storage_and_layout();

@@ -19,11 +19,9 @@
 // Every wait in the kernel is bounded: a wait that runs out records an error code in the
 // device status word, raises a CTA-wide abort flag that every other wait polls, and the CTA
 // drains its outstanding TMA copies, frees its TMEM and returns.
-#include <cuda.h>
-
 #include <mutex>
 
-#include "w4a16_async.cuh"
+#include "w4a16_umma.cuh"
 
 namespace kiln {
 namespace {
@@ -58,67 +56,6 @@ struct PrefillParams {
     unsigned long long wait_limit_ns;  // every bounded wait of the launch gives up after this long
     int test_drop_a_load;  // test hook: the activation tile of this K-step (counted per CTA) is announced but never copied; -1 = off
 };
-
-// ---- PTX wrappers ------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-// One 2-D tile shared memory -> global through the tensor map (asynchronous; completion is tracked by the thread's bulk
-// async-group).  x (elements) must be a multiple of 8 for bf16; rows or columns past the tensor's extent are clipped.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// the issuing thread's bulk stores have finished READING shared memory (the source may be overwritten)
-__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// ... and have been written out completely
-__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-        "%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, 128B-swizzled operand tile: rows of 64 bf16 (128 B), 8-row atoms 1024 B apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address
-    d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused for swizzled K-major)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset: 8 rows * 128 B
-    d |= static_cast<uint64_t>(1) << 46;                      // descriptor version for sm_100
-    d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
-    return d;
-}
 
 // Hands a CTA its work.  Default: units (tile, K-split) dealt round-robin.  Stream-K (hybrid): the tiles that fill
 // whole waves of the grid are dealt round-robin as above; the flattened (tile, K-step) space of the remaining
@@ -491,23 +428,31 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 return ld_stream_v4(reinterpret_cast<const uint4 *>(
                     p.S + static_cast<size_t>(g) * p.n + (nt * kChunksPerTile + dw % kChunksPerTile) * 64 + 8 * c));
             };
-            uint4 sv_next = make_uint4(0, 0, 0, 0);
-            int next_group = -1;
             // this team's K-steps of the piece: those whose stage number is congruent to `team`
             const int kf = ki0 + static_cast<int>((static_cast<uint32_t>(team) + DG - it_base % DG) % DG);
-            if (!p.per_column && kf < ki1) {
-                next_group = kf >> 1;
-                sv_next = load_scales(next_group);
+            // Packed words and scales of this team's next three K-steps are always in flight, each step's in registers of
+            // its own: the loop below is unrolled three times so that no register with a pending load is ever copied (a
+            // copy would wait for the load and shrink the three round trips in flight to one).
+            Regs rw[3];
+            uint4 rs[3];
+#pragma unroll
+            for (int u = 0; u < 3; ++u) {
+                rs[u] = make_uint4(0, 0, 0, 0);
+                if (kf + u * DG < ki1) {
+                    load_regs(rw[u], kf + u * DG);
+                    if (!p.per_column) rs[u] = load_scales((kf + u * DG) >> 1);
+                }
             }
-            Regs r0, r1, r2;  // packed words of this team's next three K-steps: three L2 round trips in flight
-            if (kf < ki1) load_regs(r0, kf);
-            if (kf + DG < ki1) load_regs(r1, kf + DG);
-            if (kf + 2 * DG < ki1) load_regs(r2, kf + 2 * DG);
-            for (int ki = kf; ki < ki1; ki += DG) {
+            for (int kb = kf; kb < ki1 && ok; kb += 3 * DG) {
+#pragma unroll
+            for (int u = 0; u < 3; ++u) {
+                const int ki = kb + u * DG;
+                if (ki >= ki1) break;
+                Regs &r0 = rw[u];
                 const uint32_t it = it_base + static_cast<uint32_t>(ki - ki0);
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1;
-                // scales of this K group (all blocks of a warp share one chunk: blk % kChunksPerTile == dw % ..)
+                // scales of this K-step's group (all blocks of a warp share one chunk: blk % kChunksPerTile == dw % ..)
                 const int g = p.per_column ? 0 : (ki >> 1);
                 if (g != cur_group) {
                     cur_group = g;
@@ -515,13 +460,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
                         for (int t = 0; t < 8; ++t) s2[t] = 0x3F803F80u;  // bf16x2 {1, 1}; scale applied in the epilogue
                     } else {
-                        // the scales of this group were requested when the previous group started
-                        const uint4 sv = (next_group == g) ? sv_next : load_scales(g);
-                        if (ki + DG < ki1 && ((ki + DG) >> 1) != g) {  // the group of this team's next K-step
-                            sv_next = load_scales((ki + DG) >> 1);
-                            next_group = (ki + DG) >> 1;
-                        }
-                        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+                        const uint32_t sw[4] = {rs[u].x, rs[u].y, rs[u].z, rs[u].w};
 #pragma unroll
                         for (int t = 0; t < 8; ++t) {
                             const float f = __half2float(__ushort_as_half(
@@ -570,9 +509,11 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 // warp behind a __syncwarp was measured slower: 1154 vs 1217 TFLOP/s on gate+up M=8192)
                 fence_proxy_async_smem();
                 mbar_arrive(full_b(s));
-                r0 = r1;
-                r1 = r2;
-                if (ki + 3 * DG < ki1) load_regs(r2, ki + 3 * DG);
+                if (ki + 3 * DG < ki1) {
+                    load_regs(rw[u], ki + 3 * DG);
+                    if (!p.per_column) rs[u] = load_scales((ki + 3 * DG) >> 1);
+                }
+            }
             }
             it_base += static_cast<uint32_t>(ki1 - ki0);
         }
@@ -772,43 +713,6 @@ PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool 
                 }
             }
     return best;
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
-cudaLaunchAttribute pdl_attribute() {
-    cudaLaunchAttribute a = {};
-    a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    a.val.programmaticStreamSerializationAllowed = 1;
-    return a;
-}
-
-// launches a small follow-up kernel (split-K reduction, stream-K fix-up) with programmatic dependent launch
-template <class... KArgs, class... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr = pdl_attribute();
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Tensor map of the bf16 result [m, n] for the epilogue's TMA stores: boxes of 32 rows x 64 columns, 128-byte swizzle.

@@ -136,9 +136,10 @@ void kiln_w4a16_noalloc_plan(int m, int n, int k, int out[4]);
  * columns + ncclAllGather of the slices".  B [k/16, 2*n_local] and s [k/g, n_local] are this rank's column
  * slice.  C_peers is a HOST array of n_peers (1..8) device pointers, one per GPU of the group (this GPU's
  * own buffer included), each a row-major bf16 [m, ldc] buffer mapped into this process (peer access /
- * symmetric memory).  The tcgen05 kernel stores every finished 16-byte piece of rows x columns
- * [col0, col0 + n_local) into all of them with plain stores over NVLink; no TMA and no multicast is
- * involved.  The call returns when the launch is enqueued; the gathered matrix is complete on a GPU once
+ * symmetric memory).  The tcgen05 kernel writes rows x columns [col0, col0 + n_local) of every finished tile into
+ * all of them: the buffer that lives on the current device (found with cudaPointerGetAttributes; exactly one is
+ * expected, else it is treated like the others) through the kernel's ordinary TMA-store path, the other GPUs' buffers
+ * with plain 16-byte stores over NVLink; no TMA touches another GPU's memory and no multicast is involved.  The call returns when the launch is enqueued; the gathered matrix is complete on a GPU once
  * every rank's launch has finished, so callers follow it with a stream-ordered barrier across the group
  * (kiln_b200.shard does).  ldc and col0 are in elements and multiples of 8. */
 kiln_w4a16_status_t kiln_w4a16_gemm_bf16_allgather(const void *A, const void *B, const void *s, int m, int n_local,

@@ -29,8 +29,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kDequantWarp0 = 6;
-constexpr uint32_t kEpiPitch = 144;                 // bytes per staged epilogue row (128 + 16 against bank conflicts)
-constexpr uint32_t kEpiWarpBytes = 32 * kEpiPitch;  // per epilogue warp: 32 rows x 64 columns of bf16
+constexpr uint32_t kEpiWarpBytes = 4096;  // per epilogue warp: 32 rows x 64 columns of bf16, 128B-swizzled (four 1024-byte atoms)
 constexpr int kNumEpilogueThreads = 4 * 32;
 
 struct PrefillParams {
@@ -46,6 +45,7 @@ struct PrefillParams {
     // [m, ldc] buffer of each peer GPU (peer_c[i], plain peer-mapped pointers) at column offset col0
     __nv_bfloat16 *peer_c[8];
     int n_peers, ldc, col0;
+    int self_peer;  // index in peer_c of the buffer that lives on this GPU (written through the TMA store), or -1
     // mc_c != nullptr: one multimem.st per piece to the group's multicast address instead (the switch replicates
     // the store into every GPU's buffer, this GPU's included, so each tile leaves this GPU once)
     __nv_bfloat16 *mc_c;
@@ -282,9 +282,14 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 // of round i+1 are issued as soon as the registers of round i are in shared memory, so their latency
                 // hides behind the stores, and the accumulator is handed back to the MMA issuer right after the
                 // last load has landed, not after the last store.
-                const uint32_t epi = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;
-                const bool local_out = p.n_peers == 0 && !p.mc_c;
-                const uint32_t epi_tma = epi_base + static_cast<uint32_t>(warp - 2) * 4096u;  // 1024-byte aligned swizzle atoms
+                // This GPU's own copy of the result (the only copy when the all-gather is not fused) leaves through one
+                // asynchronous TMA store of the 32 x 64 tile per round; copies for other GPUs (fused all-gather) are read
+                // back from the same tile and stored over NVLink, 128 contiguous bytes of four rows per instruction, or
+                // once through the NVSwitch multicast address.
+                const bool tma_out = (p.n_peers == 0 && !p.mc_c) || p.self_peer >= 0;
+                const bool remote_out = p.mc_c || p.n_peers > (p.self_peer >= 0 ? 1 : 0);
+                const uint32_t epi_tma = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;  // 1024-byte aligned swizzle atoms
+                const int x0_out = (p.n_peers > 0 ? p.col0 : 0) + nt * BN;  // first column of the tile in the output buffer
                 uint32_t ra[32], rb[32];
                 tmem_ld_32x32b_x32(t_row, ra);
                 tmem_ld_32x32b_x32(t_row + 32, rb);
@@ -309,17 +314,11 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                                 __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
                                 o[e] = *reinterpret_cast<uint32_t *>(&b);
                             }
-                            if (local_out) {
-                                // 128-byte rows, 16-byte chunk index XOR (row % 8): the layout of the 128B-swizzled tensor map
-                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                                                 epi_tma + lane * 128 + (((half * 4 + v) ^ (lane & 7)) << 4)),
-                                             "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                             : "memory");
-                            } else {
-                                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(epi + lane * kEpiPitch + half * 64 + v * 16),
-                                             "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                             : "memory");
-                            }
+                            // 128-byte rows, 16-byte chunk index XOR (row % 8): the layout of the 128B-swizzled tensor map
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
+                                             epi_tma + lane * 128 + (((half * 4 + v) ^ (lane & 7)) << 4)),
+                                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                         : "memory");
                         }
                     }
                     if (pp + 1 < BN / 64) {
@@ -329,45 +328,42 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         tc_fence_before();
                         mbar_arrive(tmem_empty(acc));  // every column of this accumulator is in registers or shared memory
                     }
-                    if (local_out) {
-                        // this GPU's own C: one asynchronous TMA store of the 32 x 64 tile per round (full 128-byte lines, no
-                        // load back from shared memory, nothing for this warp to wait for until it reuses the tile)
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            tma_store_2d(&tmap_c, epi_tma, nt * BN + pp * 64, (mt * MT + h) * BM + quarter * 32);
-                            bulk_commit_group();
-                            bulk_wait_group_read0();  // (the next round's TMEM loads are already in flight)
-                        }
-                        __syncwarp();
-                        continue;
-                    }
+                    if (tma_out) fence_proxy_async_smem();
                     __syncwarp();
-                    const int piece = lane & 7;
-                    const int col_out = nt * BN + pp * 64 + piece * 8;
+                    if (tma_out && lane == 0) {
+                        // (full 128-byte lines, no load back from shared memory; rows past m are clipped by the tensor map)
+                        tma_store_2d(&tmap_c, epi_tma, x0_out + pp * 64, (mt * MT + h) * BM + quarter * 32);
+                        bulk_commit_group();
+                    }
+                    if (remote_out) {
+                        const int piece = lane & 7;
+                        const int col_out = p.col0 + nt * BN + pp * 64 + piece * 8;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int rl = i * 4 + (lane >> 3);
-                        const int grow = (mt * MT + h) * BM + quarter * 32 + rl;
-                        uint4 val;
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
-                                     : "r"(epi + rl * kEpiPitch + piece * 16));
-                        if (grow < p.m) {
-                            if (p.mc_c) {
-                                asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(
-                                                 p.mc_c + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out),
-                                             "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
-                                             : "memory");
-                            } else if (p.n_peers == 0) {
-                                *reinterpret_cast<uint4 *>(p.C + static_cast<size_t>(grow) * p.n + col_out) = val;
-                            } else {
-                                // column-parallel all-gather fused into the epilogue: plain stores into every GPU's buffer
-                                for (int pe = 0; pe < p.n_peers; ++pe)
-                                    *reinterpret_cast<uint4 *>(p.peer_c[pe] + static_cast<size_t>(grow) * p.ldc + p.col0 + col_out) = val;
+                        for (int i = 0; i < 8; ++i) {
+                            const int rl = i * 4 + (lane >> 3);
+                            const int grow = (mt * MT + h) * BM + quarter * 32 + rl;
+                            uint4 val;
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                         : "r"(epi_tma + rl * 128 + ((piece ^ (rl & 7)) << 4)));
+                            if (grow < p.m) {
+                                if (p.mc_c) {
+                                    asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(
+                                                     p.mc_c + static_cast<size_t>(grow) * p.ldc + col_out),
+                                                 "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                                                 : "memory");
+                                } else {
+                                    // column-parallel all-gather fused into the epilogue: plain stores into the other GPUs' buffers
+                                    for (int pe = 0; pe < p.n_peers; ++pe)
+                                        if (pe != p.self_peer)
+                                            *reinterpret_cast<uint4 *>(p.peer_c[pe] + static_cast<size_t>(grow) * p.ldc + col_out) = val;
+                                }
                             }
                         }
                     }
+                    // the tile is rewritten in the next round: the TMA store has read it (the next round's TMEM loads are
+                    // already in flight), and so has every lane
+                    if (tma_out && lane == 0) bulk_wait_group_read0();
                     __syncwarp();
                 }
                 continue;  // the accumulator was released above
@@ -797,8 +793,27 @@ int launch_prefill(const GemmArgs &a) {
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return KILN_W4A16_ERR_CUDA;
-    CUtensorMap tmap_c;  // (only used when the result goes to this GPU's own C)
-    if (!encode_c_map(enc, &tmap_c, a.C, a.m, a.n)) return KILN_W4A16_ERR_CUDA;
+    // Which of the fused all-gather's buffers lives on this GPU: that copy leaves through the TMA-store path.
+    int self_peer = -1;
+    if (a.n_peers > 0) {
+        int dev = -1, found = 0;
+        cudaGetDevice(&dev);
+        for (int i = 0; i < a.n_peers && i < 8; ++i) {
+            cudaPointerAttributes at;
+            if (cudaPointerGetAttributes(&at, a.peer_c[i]) == cudaSuccess && at.type == cudaMemoryTypeDevice && at.device == dev) {
+                self_peer = i;
+                ++found;
+            }
+        }
+        cudaGetLastError();  // (an unregistered pointer only means "not ours")
+        if (found != 1) self_peer = -1;  // ambiguous: every copy goes through the store path of the remote copies
+    }
+    CUtensorMap tmap_c;  // this GPU's own C: [m, n], or its [m, ldc] buffer of the fused all-gather
+    if (self_peer >= 0) {
+        if (!encode_c_map(enc, &tmap_c, a.peer_c[self_peer], a.m, a.ldc)) return KILN_W4A16_ERR_CUDA;
+    } else if (!encode_c_map(enc, &tmap_c, a.C, a.m, a.n)) {
+        return KILN_W4A16_ERR_CUDA;
+    }
 
     PrefillParams p{};
     p.B = static_cast<const uint4 *>(a.B);
@@ -817,6 +832,7 @@ int launch_prefill(const GemmArgs &a) {
     p.n_peers = a.n_peers;
     p.ldc = a.ldc;
     p.col0 = a.col0;
+    p.self_peer = self_peer;
     p.mc_c = static_cast<__nv_bfloat16 *>(a.mc_c);
     for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;
@@ -982,6 +998,7 @@ extern "C" kiln_w4a16_status_t kiln_w4a16_gemm_bf16_noalloc(const void *A, const
     p.per_column = groupsize == -1;
     p.wait_limit_ns = g_wait_limit_ns;
     p.test_drop_a_load = -1;
+    p.self_peer = -1;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     CUtensorMap tmap_c;
     if (!encode_c_map(enc, &tmap_c, C, m, n)) return KILN_W4A16_ERR_CUDA;

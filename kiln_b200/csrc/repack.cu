@@ -302,6 +302,76 @@ __global__ void pack_words_kernel(const void *w, int n, int g, const float *scal
     b_packed[static_cast<size_t>(kb) * 2 * n + ch * 128 + tid] = static_cast<int32_t>(word);
 }
 
+// Grouped mode (128 rows per scale), everything in one pass: one block per (scale group, 64-column chunk) reads its
+// 128 x 64 weights once (16-byte loads, 128 contiguous bytes per row), finds the column maxima, writes the 64 fp16
+// scales at their Marlin positions and the eight 512-byte packed blocks.  Same arithmetic as the two kernels above.
+// grid = (n/64, k/128), block = 256.
+template <bool BF16>
+__global__ void __launch_bounds__(256) pack_group_kernel(const void *w, int n, uint16_t *scales_perm, int32_t *b_packed, float *dequant) {
+    __shared__ float tile[128][65];
+    __shared__ float part_max[4][64];
+    __shared__ float s_col[64];
+    const int ch = blockIdx.x, grp = blockIdx.y, tid = threadIdx.x;
+    const size_t row0 = static_cast<size_t>(grp) * 128;
+    // 128 rows x 8 pieces of 8 weights
+    for (int e = tid; e < 128 * 8; e += 256) {
+        const int r = e >> 3, p8 = e & 7;
+        const size_t off = (row0 + r) * n + ch * 64 + p8 * 8;
+        float v[8];
+        if (BF16) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(w) + off);
+            const uint32_t x[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(x[i] << 16);
+                v[2 * i + 1] = __uint_as_float(x[i] & 0xFFFF0000u);
+            }
+        } else {
+            const float4 a = *reinterpret_cast<const float4 *>(static_cast<const float *>(w) + off);
+            const float4 b = *reinterpret_cast<const float4 *>(static_cast<const float *>(w) + off + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tile[r][p8 * 8 + i] = v[i];
+    }
+    __syncthreads();
+    {
+        const int col = tid & 63, part = tid >> 6;
+        float mx = 0.f;
+        for (int r = 0; r < 32; ++r) mx = fmaxf(mx, fabsf(tile[part * 32 + r][col]));
+        part_max[part][col] = mx;
+    }
+    __syncthreads();
+    if (tid < 64) {
+        float mx = fmaxf(fmaxf(part_max[0][tid], part_max[1][tid]), fmaxf(part_max[2][tid], part_max[3][tid]));
+        if (mx == 0.f) mx = 1.f;
+        const __half h = __float2half_rn(__fdiv_rn(2.0f * mx, 15.0f));
+        scales_perm[static_cast<size_t>(grp) * n + scale_group_pos(ch * 64 + tid)] = __half_as_ushort(h);
+        s_col[tid] = __half2float(h);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 8 * 128; idx += 256) {
+        const int kt = idx >> 7, t128 = idx & 127;
+        const int lane = t128 >> 2, j = t128 & 3;
+        const int r0 = kt * 16 + 2 * (lane & 3), c = lane >> 2;
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int cc = 16 * j + c + nib_dc(i);
+            word |= static_cast<uint32_t>(quantize_one(tile[r0 + nib_dr(i)][cc], s_col[cc])) << (4 * i);
+        }
+        b_packed[(static_cast<size_t>(grp) * 8 + kt) * 2 * n + ch * 128 + t128] = static_cast<int32_t>(word);
+    }
+    if (dequant) {
+        for (int e = tid; e < 128 * 64; e += 256) {
+            const int r = e >> 6, c = e & 63;
+            const float sc = s_col[c];
+            dequant[(row0 + r) * n + ch * 64 + c] = __fmul_rn(static_cast<float>(quantize_one(tile[r][c], sc) - kQOffset), sc);
+        }
+    }
+}
+
 // Already-quantised input: q uint8 [k,n] -> packed words; scales moved to Marlin order.
 __global__ void repack_words_kernel(const uint8_t *q, int n, int32_t *b_packed) {
     __shared__ uint8_t nib[16][64];
@@ -373,6 +443,16 @@ kiln_w4a16_status_t kiln_w4a16_quantize_and_pack_device(const void *weight, int 
     if (!weight || !b_packed || !scales_f16) return KILN_W4A16_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int num_groups = k / g;
+    if (groupsize == 128 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0) {  // (n is a multiple of 64: rows stay 16-byte aligned)
+        const dim3 grid(n / 64, k / 128);
+        if (weight_is_bf16)
+            pack_group_kernel<true><<<grid, 256, 0, st>>>(weight, n, scales_f16, b_packed, dequant);
+        else
+            pack_group_kernel<false><<<grid, 256, 0, st>>>(weight, n, scales_f16, b_packed, dequant);
+        pack_fence_kernel<<<1, 32, 0, st>>>();
+        note_launch(2);
+        return record_cuda_error(cudaGetLastError());
+    }
     float *scales_nat = nullptr;  // natural-order f32 scales, scratch for the second kernel
     if (int rc = record_cuda_error(cudaMallocAsync(&scales_nat, sizeof(float) * num_groups * n, st))) return rc;
     const dim3 g1(n / 128, num_groups), g2(n / 64, k / 16);

@@ -40,6 +40,31 @@ def test_device_pack_f32_bit_exact(cuda_device, k, n, gs):
         assert (p == po).all() and (s == so.view(np.uint16)).all() and (d == do).all()
 
 
+def test_device_pack_unaligned_weight_takes_the_two_kernel_path(cuda_device):
+    """A weight that does not start on a 16-byte boundary cannot use the one-pass kernel's vector loads."""
+    k, n = 256, 256
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+    flat = torch.zeros(k * n + 1, dtype=torch.float32, device=cuda_device)
+    flat[1:] = torch.from_numpy(w).to(cuda_device).reshape(-1)
+    p, s, d = _dev_pack(flat[1:].view(k, n), 128)
+    p2, s2, d2 = kiln_b200.pack.quantize_and_pack(w, k, n, 128)
+    assert (p == p2).all() and (s == s2.view(np.uint16)).all() and (d == d2).all()
+
+
+def test_device_pack_bf16_full_size(cuda_device):
+    """One gate projection (2560 x 9216, bf16, grouped) through the one-pass kernel against the host packer."""
+    k, n = 2560, 9216
+    w = (torch.randn(k, n, generator=torch.Generator().manual_seed(11)) * 0.02).to(torch.bfloat16)
+    w[5, :] *= 40
+    w[:, 7] = 0
+    proj = kiln_b200.pack_from_bf16(w.to(cuda_device), 128)
+    torch.cuda.synchronize()
+    p2, s2, _ = kiln_b200.pack.quantize_and_pack(w.float().numpy(), k, n, 128)
+    assert (proj.b_packed.cpu().numpy() == p2).all()
+    assert (proj.scales.cpu().view(torch.int16).numpy().view(np.uint16) == s2.view(np.uint16)).all()
+
+
 def test_device_pack_bf16_and_proj_helper(cuda_device):
     k, n = 2560, 1024
     w = (torch.randn(k, n, generator=torch.Generator().manual_seed(3)) * 0.05).to(torch.bfloat16)

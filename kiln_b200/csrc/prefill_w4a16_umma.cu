@@ -619,21 +619,21 @@ struct PrefillConfig {
     int bn, splits, mt, stream_k;
 };
 
-// Cost model of one launch, least-squares fitted (mean error 5 %) to 640 timed launches on B200: 5 projection shapes x
-// M = 64..8192 x 18 tilings, each timed alone after an L2 flush.  Microseconds:
+// Cost model of one launch, least-squares fitted (mean error 6 %) to 1100 timed launches on B200: 5 projection shapes x
+// M = 64..8192 x every tiling the rule considers, each timed alone after an L2 flush.  Microseconds:
 //   launch + waves * (K-steps per unit * step + tile) [+ split-K: fixed + per MB of fp32 slab traffic]
 //   stream-K: launch + whole waves as above + share * step + 2 * tile + per MB of remainder tiles + per slab piece
 // `step` is the time of one 64-K step of a CTA, `tile` what a tile adds on top (epilogue that does not overlap, pipeline
 // restart); both depend on the columns per tile and the M-tiles per stage.  On the fitted set the model's choice is
-// within 0.4 % of the best measured tiling in total.
+// within 0.2 % of the best measured tiling in total.
 struct TileCost {
     double step, tile;
 };
 TileCost tile_cost(int bn, int mt) {
-    if (mt == 2) return bn == 256 ? TileCost{0.671, 7.69} : TileCost{0.539, 0.85};
-    return bn == 256 ? TileCost{0.629, 1.83} : TileCost{0.467, 0.18};
+    if (mt == 2) return bn == 256 ? TileCost{0.594, 11.45} : TileCost{0.466, 4.00};
+    return bn == 256 ? TileCost{0.488, 5.16} : TileCost{0.399, 1.72};
 }
-constexpr double kCostLaunch = 11.0, kCostSplitFixed = 3.30, kCostSplitPerMB = 0.409, kCostSkPerMB = 0.688, kCostSkPerPiece = 0.107;
+constexpr double kCostLaunch = 7.99, kCostSplitFixed = 3.33, kCostSplitPerMB = 0.316, kCostSkPerMB = 0.181, kCostSkPerPiece = 0.135;
 
 // Stream-K split of `tiles` tiles over `grid` CTAs: the tiles of the whole waves are dealt round-robin, the K-steps of
 // the rest go in equal shares to `ctas` CTAs.  A share is at least 8 K-steps and at least 1/36 of a tile, so that no tile

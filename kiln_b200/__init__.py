@@ -4,7 +4,7 @@ Host-side mirror of the reference crate's public surface
 (kiln-marlin-gemm/src/lib.rs: `marlin_w4a16_gemm`, `mod pack`) and of its caller-side
 helpers (kiln-model/src/marlin_proj.rs), on top of the C ABI in include/kiln_w4a16.h.
 """
-from . import pack  # noqa: F401
+from . import nvtx, pack  # noqa: F401
 from .marlin_gemm import KilnMarlinError, marlin_w4a16_gemm, workspace_bytes  # noqa: F401
 from .shard import (  # noqa: F401
     ColumnParallelLinear,

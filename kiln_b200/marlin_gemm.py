@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, nvtx
 
 
 class KilnMarlinError(RuntimeError):
@@ -82,7 +82,7 @@ def marlin_w4a16_gemm(a: torch.Tensor, b_packed: torch.Tensor, scales: torch.Ten
         raise KilnMarlinError("kiln-marlin-gemm: out must be a contiguous bf16 [m, n] tensor on a's device")
     if m == 0:
         return out
-    with torch.cuda.device(a.device):
+    with torch.cuda.device(a.device), nvtx.range("kiln/marlin/gemm"):
         nbytes = workspace_bytes(m, n, k)
         ws = _workspace(a.device, nbytes) if nbytes else None
         stream = torch.cuda.current_stream(a.device).cuda_stream

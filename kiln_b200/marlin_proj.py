@@ -7,7 +7,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from . import _lib
+from . import _lib, nvtx
 from .marlin_gemm import KilnMarlinError, marlin_w4a16_gemm
 
 
@@ -55,7 +55,7 @@ def pack_from_bf16(weight_t: torch.Tensor, groupsize: int = 128) -> Optional[Mar
     dev = w.device
     b_packed = torch.empty((k // 16, 2 * n), dtype=torch.int32, device=dev)
     scales = torch.empty((k // g, n), dtype=torch.float16, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), nvtx.range("kiln/marlin/pack"):
         rc = _lib.lib().kiln_w4a16_quantize_and_pack_device(
             w.data_ptr(), 1 if w.dtype == torch.bfloat16 else 0, k, n, groupsize,
             b_packed.data_ptr(), scales.data_ptr(), None, torch.cuda.current_stream(dev).cuda_stream,
@@ -237,7 +237,8 @@ def _gemm_ex(x2: torch.Tensor, proj: MarlinPackedProj, swiglu: bool, lora_a, lor
     if m == 0:
         return out
     lib = _lib.lib()
-    with torch.cuda.device(x2.device):
+    name = "kiln/mlp/gate_up_swiglu" if swiglu else ("kiln/marlin/gemm_lora" if lora_a is not None else "kiln/marlin/gemm")
+    with torch.cuda.device(x2.device), nvtx.range(name):
         need = int(lib.kiln_w4a16_workspace_bytes_ex(m, proj.n, k, ctypes.byref(ep)))
         ws = _ex_workspaces.get(x2.device)
         if need and (ws is None or ws.numel() < need):
@@ -308,7 +309,7 @@ def grouped_matmul_bf16(xs: Sequence[torch.Tensor], projs: Sequence[MarlinPacked
         arr[i] = _lib.Problem(xc.data_ptr(), pr.b_packed.data_ptr(), o.data_ptr(), pr.scales.data_ptr(), x.shape[0], pr.n, pr.k,
                               pr.groupsize)
         need = max(need, int(lib.kiln_w4a16_workspace_bytes(x.shape[0], pr.n, pr.k)))
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), nvtx.range("kiln/proj/grouped"):
         ws = _ex_workspaces.get(dev)
         if need and (ws is None or ws.numel() < need):
             ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)

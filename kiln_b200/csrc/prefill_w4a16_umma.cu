@@ -129,7 +129,7 @@ struct Cfg {
     static_assert(kBlocksPerStage % kGroupWarps == 0 && kGroupWarps % (BN / 64) == 0,
                   "a dequant team must divide the packed blocks of a stage and keep one chunk per warp");
     static constexpr int kBarrierBytes = 1024;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 4 * kEpiWarpBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 4 * 2 * kEpiWarpBytes + 1024;  // + alignment slack
     // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
     static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                        (static_cast<uint32_t>(BM >> 4) << 24);
@@ -288,13 +288,15 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 // once through the NVSwitch multicast address.
                 const bool tma_out = (p.n_peers == 0 && !p.mc_c) || p.self_peer >= 0;
                 const bool remote_out = p.mc_c || p.n_peers > (p.self_peer >= 0 ? 1 : 0);
-                const uint32_t epi_tma = epi_base + static_cast<uint32_t>(warp - 2) * kEpiWarpBytes;  // 1024-byte aligned swizzle atoms
+                // two staging tiles per warp, used in turn: the TMA store of one round reads its tile while the next round fills the other
+                const uint32_t epi_tma0 = epi_base + static_cast<uint32_t>(warp - 2) * (2 * kEpiWarpBytes);  // 1024-byte aligned swizzle atoms
                 const int x0_out = (p.n_peers > 0 ? p.col0 : 0) + nt * BN;  // first column of the tile in the output buffer
                 uint32_t ra[32], rb[32];
                 tmem_ld_32x32b_x32(t_row, ra);
                 tmem_ld_32x32b_x32(t_row + 32, rb);
 #pragma unroll 1
                 for (int pp = 0; pp < BN / 64; ++pp) {
+                    const uint32_t epi_tma = epi_tma0 + static_cast<uint32_t>(pp & 1) * kEpiWarpBytes;
                     tmem_ld_wait();
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
@@ -361,9 +363,9 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                             }
                         }
                     }
-                    // the tile is rewritten in the next round: the TMA store has read it (the next round's TMEM loads are
-                    // already in flight), and so has every lane
-                    if (tma_out && lane == 0) bulk_wait_group_read0();
+                    // this tile is rewritten two rounds from now: the TMA store of the round before this one has read the
+                    // other tile (the next round's TMEM loads are already in flight), and every lane is done with this one
+                    if (tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     __syncwarp();
                 }
                 continue;  // the accumulator was released above

@@ -112,18 +112,23 @@ struct WorkIter {
 // accumulators then take both TMEM buffers, so the epilogue only partly overlaps the next tile.
 // DG = dequant groups: the DW dequant warps are split into DG teams that fill alternate stages, so the
 // dequant of stage s+1 runs beside that of stage s instead of after it.
-template <int BN, int MT = 1, int DW = 8, int DG = 2>
+// KP = MMA issuers per M-tile: with KP = 2 (128-column tiles of one M-tile, which are bound by the ~105 cycles one thread
+// needs per tcgen05.mma) a second warp issues the upper two of a K-step's four MMAs into an accumulator of its own, and
+// the epilogue adds the two accumulators.
+template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1>
 struct Cfg {
+    static_assert(KP == 1 || (KP == 2 && MT == 1 && BN == 128), "K-parity issuers: one M-tile of 128 columns only");
+    static constexpr int kIssuers = MT == 2 ? 2 : KP;
     static constexpr int kGroupWarps = DW / DG;
     // producer, MMA, 4 epilogue and DW dequant warps (16 dequant warps were measured no faster than 8)
     // MT == 2 adds a second MMA-issuing warp (the last one): each issuer owns one M-tile of the pair
     static constexpr int kMmaWarp2 = 6 + DW;
-    static constexpr int kThreads = (6 + DW + (MT == 2 ? 1 : 0)) * 32;
+    static constexpr int kThreads = (6 + DW + (kIssuers == 2 ? 1 : 0)) * 32;
     static constexpr int kABytes = MT * BM * BK * 2;  // 16 KB per M-tile
     static constexpr int kStages = (192 * 1024) / (kABytes + BN * BK * 2);
     static constexpr int kBBytes = BN * BK * 2;  // 32 / 16 KB
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kTmemCols = 2 * BN * KP;
     static constexpr int kBlocksPerStage = (BN / 64) * 4;  // 512-byte packed blocks per stage
     static constexpr int kBlocksPerWarp = kBlocksPerStage / kGroupWarps;
     static_assert(kBlocksPerStage % kGroupWarps == 0 && kGroupWarps % (BN / 64) == 0,
@@ -140,11 +145,11 @@ struct DequantRegs {
     uint4 w[NBLK];
 };
 
-template <int BN, int MT, int DW, int DG>
-__global__ void __launch_bounds__((6 + DW + (MT == 2 ? 1 : 0)) * 32, 1)
+template <int BN, int MT, int DW, int DG, int KP>
+__global__ void __launch_bounds__((6 + DW + ((MT == 2 || KP == 2) ? 1 : 0)) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
                      const PrefillParams p) {
-    using C = Cfg<BN, MT, DW, DG>;
+    using C = Cfg<BN, MT, DW, DG, KP>;
     using Regs = DequantRegs<C::kBlocksPerWarp>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -166,10 +171,10 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int s = 0; s < C::kStages; ++s) {
             // one "stage full" barrier: the TMA producer (1 arrival + the tile's bytes) and the threads of the dequant team
             mbar_init(full_a(s), 1 + C::kGroupWarps * 32);
-            mbar_init(empty(s), MT);  // one tcgen05.commit per MMA issuer
+            mbar_init(empty(s), C::kIssuers);  // one tcgen05.commit per MMA issuer
         }
         for (int a = 0; a < 2; ++a) {
-            mbar_init(tmem_full(a), 1);
+            mbar_init(tmem_full(a), KP);  // one tcgen05.commit per issuer that writes into this buffer
             mbar_init(tmem_empty(a), kNumEpilogueThreads);
         }
         *abort_flag = 0;
@@ -221,14 +226,18 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 }
             }
         }
-    } else if (warp == 1 || (MT == 2 && warp == C::kMmaWarp2)) {
+    } else if (warp == 1 || (C::kIssuers == 2 && warp == C::kMmaWarp2)) {
         // ---------------- MMA issuer(s) ----------------
         // One thread issues about one tcgen05.mma per ~105 cycles and spends ~400 more per K-step on the
         // barrier waits and the commit, which is more than the 1024 cycles the eight 128 x 256 x 16 MMAs of a
         // pair execute in.  With MT == 2 the two M-tiles therefore have one issuer each (warp 1: tile 0, the
-        // last warp: tile 1); their MMAs go to different accumulators and need no order between them.
+        // last warp: tile 1); their MMAs go to different accumulators and need no order between them.  With
+        // KP == 2 (one M-tile of 128 columns, whose four MMAs per K-step execute in 256 cycles) the two issuers
+        // share the K-step instead: warp 1 issues MMAs 0 and 1, the last warp MMAs 2 and 3, each into an
+        // accumulator of its own, and the epilogue adds the two (gate+up M=64: 20.6 -> 18.7 us).
         if (lane == 0) {
             const int h0 = (MT == 2 && warp != 1) ? 1 : 0, h1 = MT == 2 ? h0 + 1 : 1;
+            const int q = (KP == 2 && warp != 1) ? 1 : 0;  // K-parity issuer: MMAs 2q, 2q+1 of every K-step, accumulator q
             uint32_t it = 0, tile = 0;
             bool ok = true;
             WorkIter wi(p);
@@ -249,8 +258,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         }
                         const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes + h * (BM * BK * 2));
 #pragma unroll
-                        for (int kk = 0; kk < BK / 16; ++kk)
-                            umma_bf16(tmem_base + acc * BN, a_desc + 2 * kk, b_desc + 2 * kk, C::kIdesc,
+                        for (int kk = 0; kk < BK / 16 / KP; ++kk)
+                            umma_bf16(tmem_base + (acc * KP + q) * BN, a_desc + 2 * (kk + 2 * q), b_desc + 2 * (kk + 2 * q), C::kIdesc,
                                       (ki > ki0 || kk > 0) ? 1u : 0u);
                         if (ki == ki1 - 1) umma_commit(tmem_full(acc));  // accumulator h is complete
                     }
@@ -274,7 +283,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (!(ok = mbar_wait(tmem_full(acc), acc_ph, abort_flag, p.status, 0x500u | acc, p.wait_limit_ns))) break;
             tc_fence_after();
             const int row = (mt * MT + h) * BM + quarter * 32 + lane;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * KP * BN;
             if (slab < 0 && p.splits == 1) {
                 // bf16 result, 64 columns per round.  A thread owns one row of the accumulator; the 128-byte pieces go
                 // through a per-warp shared-memory tile so that the global (or peer, over NVLink) stores are 128
@@ -292,6 +301,81 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 const uint32_t epi_tma0 = epi_base + static_cast<uint32_t>(warp - 2) * (2 * kEpiWarpBytes);  // 1024-byte aligned swizzle atoms
                 const int x0_out = (p.n_peers > 0 ? p.col0 : 0) + nt * BN;  // first column of the tile in the output buffer
                 uint32_t ra[32], rb[32];
+                if constexpr (KP == 2) {
+                    // two accumulators (one per K-parity issuer) to add: 32 columns of each per half-round; the loads of the
+                    // next half-round are in flight while a finished 64-column tile is stored
+                    tmem_ld_32x32b_x32(t_row, ra);
+                    tmem_ld_32x32b_x32(t_row + BN, rb);
+#pragma unroll 1
+                    for (int hh = 0; hh < BN / 32; ++hh) {
+                        const int pp = hh >> 1, half = hh & 1;
+                        const uint32_t epi_tma = epi_tma0 + static_cast<uint32_t>(pp & 1) * kEpiWarpBytes;
+                        const int col = nt * BN + hh * 32;
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float x0 = __uint_as_float(ra[8 * v + 2 * e]) + __uint_as_float(rb[8 * v + 2 * e]);
+                                float x1 = __uint_as_float(ra[8 * v + 2 * e + 1]) + __uint_as_float(rb[8 * v + 2 * e + 1]);
+                                if (p.per_column) {
+                                    const int pos = scale_single_pos(col + 8 * v + 2 * e);
+                                    x0 *= __half2float(p.S[pos]);
+                                    x1 *= __half2float(p.S[pos + 1]);
+                                }
+                                __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
+                                o[e] = *reinterpret_cast<uint32_t *>(&b);
+                            }
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
+                                             epi_tma + lane * 128 + (((half * 4 + v) ^ (lane & 7)) << 4)),
+                                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                         : "memory");
+                        }
+                        if (hh + 1 < BN / 32) {
+                            tmem_ld_32x32b_x32(t_row + (hh + 1) * 32, ra);
+                            tmem_ld_32x32b_x32(t_row + BN + (hh + 1) * 32, rb);
+                        } else {
+                            tc_fence_before();
+                            mbar_arrive(tmem_empty(acc));  // every column of both accumulators is in registers or shared memory
+                        }
+                        if (half == 0) continue;
+                        if (tma_out) fence_proxy_async_smem();
+                        __syncwarp();
+                        if (tma_out && lane == 0) {
+                            tma_store_2d(&tmap_c, epi_tma, x0_out + pp * 64, (mt * MT + h) * BM + quarter * 32);
+                            bulk_commit_group();
+                        }
+                        if (remote_out) {
+                            const int piece = lane & 7;
+                            const int col_out = p.col0 + nt * BN + pp * 64 + piece * 8;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int rl = i * 4 + (lane >> 3);
+                                const int grow = (mt * MT + h) * BM + quarter * 32 + rl;
+                                uint4 val;
+                                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                             : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                                             : "r"(epi_tma + rl * 128 + ((piece ^ (rl & 7)) << 4)));
+                                if (grow < p.m) {
+                                    if (p.mc_c) {
+                                        asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(
+                                                         p.mc_c + static_cast<size_t>(grow) * p.ldc + col_out),
+                                                     "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                                                     : "memory");
+                                    } else {
+                                        for (int pe = 0; pe < p.n_peers; ++pe)
+                                            if (pe != p.self_peer)
+                                                *reinterpret_cast<uint4 *>(p.peer_c[pe] + static_cast<size_t>(grow) * p.ldc + col_out) = val;
+                                    }
+                                }
+                            }
+                        }
+                        if (tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        __syncwarp();
+                    }
+                    continue;  // the accumulators were released above
+                }
                 tmem_ld_32x32b_x32(t_row, ra);
                 tmem_ld_32x32b_x32(t_row + 32, rb);
 #pragma unroll 1
@@ -374,6 +458,13 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(t_row + cc * 32, r);
+                if constexpr (KP == 2) {  // add the second K-parity accumulator
+                    uint32_t r2[32];
+                    tmem_ld_32x32b_x32(t_row + BN + cc * 32, r2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+                }
                 tmem_ld_wait();
                 if (slab >= 0) {
                     // stream-K piece: tile-shaped fp32 slab, all rows (rows past m hold zeros)
@@ -627,15 +718,15 @@ struct PrefillConfig {
 //   stream-K: launch + whole waves as above + share * step + 2 * tile + per MB of remainder tiles + per slab piece
 // `step` is the time of one 64-K step of a CTA, `tile` what a tile adds on top (epilogue that does not overlap, pipeline
 // restart); both depend on the columns per tile and the M-tiles per stage.  On the fitted set the model's choice is
-// within 0.2 % of the best measured tiling in total.
+// within 0.5 % of the best measured tiling in total.
 struct TileCost {
     double step, tile;
 };
 TileCost tile_cost(int bn, int mt) {
-    if (mt == 2) return bn == 256 ? TileCost{0.594, 11.45} : TileCost{0.466, 4.00};
-    return bn == 256 ? TileCost{0.488, 5.16} : TileCost{0.399, 1.72};
+    if (mt == 2) return bn == 256 ? TileCost{0.583, 11.45} : TileCost{0.465, 3.94};
+    return bn == 256 ? TileCost{0.488, 4.93} : TileCost{0.345, 2.01};
 }
-constexpr double kCostLaunch = 7.99, kCostSplitFixed = 3.33, kCostSplitPerMB = 0.316, kCostSkPerMB = 0.181, kCostSkPerPiece = 0.135;
+constexpr double kCostLaunch = 7.36, kCostSplitFixed = 3.93, kCostSplitPerMB = 0.322, kCostSkPerMB = 0.154, kCostSkPerPiece = 0.140;
 
 // Stream-K split of `tiles` tiles over `grid` CTAs: the tiles of the whole waves are dealt round-robin, the K-steps of
 // the rest go in equal shares to `ctas` CTAs.  A share is at least 8 K-steps and at least 1/36 of a tile, so that no tile
@@ -723,14 +814,14 @@ bool encode_c_map(EncodeTiledFn enc, CUtensorMap *map, void *c, int m, int n) {
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int MT = 1, int DW = 8, int DG = 2>
+template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1>
 int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillParams &p, cudaStream_t stream) {
-    using C = Cfg<BN, MT, DW, DG>;
+    using C = Cfg<BN, MT, DW, DG, KP>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG>,
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG, KP>,
                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
             return rc;
         attr_set[dev] = true;
@@ -746,7 +837,7 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillP
     cudaLaunchAttribute attr = pdl_attribute();
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG>, tmap, tmap_c, p));
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP>, tmap, tmap_c, p));
 }
 
 }  // namespace
@@ -851,7 +942,8 @@ int launch_prefill(const GemmArgs &a) {
     if (c.mt == 2)
         rc = c.bn == 256 ? launch_bn<256, 2>(tmap, tmap_c, p, a.stream) : launch_bn<128, 2>(tmap, tmap_c, p, a.stream);
     else
-        rc = c.bn == 256 ? launch_bn<256, 1>(tmap, tmap_c, p, a.stream) : launch_bn<128, 1>(tmap, tmap_c, p, a.stream);
+        // (128-column tiles of one M-tile are bound by the MMA issue rate: two issuers, each with an accumulator of its own)
+        rc = c.bn == 256 ? launch_bn<256, 1>(tmap, tmap_c, p, a.stream) : launch_bn<128, 1, 8, 2, 2>(tmap, tmap_c, p, a.stream);
     if (rc) return rc;
     if (c.splits > 1) {
         const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;

@@ -115,21 +115,26 @@ struct WorkIter {
 // KP = MMA issuers per M-tile: with KP = 2 (128-column tiles of one M-tile, which are bound by the ~105 cycles one thread
 // needs per tcgen05.mma) a second warp issues the upper two of a K-step's four MMAs into an accumulator of its own, and
 // the epilogue adds the two accumulators.
-template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1>
+// KS = 64-deep K atoms per pipeline stage: with KS = 2 a stage holds 128 K-elements (one scale group), which halves the
+// barrier round trips, waits and commits per K of the small tiles that are bound by them.
+template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1>
 struct Cfg {
     static_assert(KP == 1 || (KP == 2 && MT == 1 && BN == 128), "K-parity issuers: one M-tile of 128 columns only");
+    static_assert(KS == 1 || KS == 2, "one or two 64-deep atoms per stage");
+    static constexpr int kAAtomBytes = MT * BM * BK * 2;  // one 64-deep atom of the activation tile(s)
+    static constexpr int kBAtomBytes = BN * BK * 2;
     static constexpr int kIssuers = MT == 2 ? 2 : KP;
     static constexpr int kGroupWarps = DW / DG;
     // producer, MMA, 4 epilogue and DW dequant warps (16 dequant warps were measured no faster than 8)
     // MT == 2 adds a second MMA-issuing warp (the last one): each issuer owns one M-tile of the pair
     static constexpr int kMmaWarp2 = 6 + DW;
     static constexpr int kThreads = (6 + DW + (kIssuers == 2 ? 1 : 0)) * 32;
-    static constexpr int kABytes = MT * BM * BK * 2;  // 16 KB per M-tile
-    static constexpr int kStages = (192 * 1024) / (kABytes + BN * BK * 2);
-    static constexpr int kBBytes = BN * BK * 2;  // 32 / 16 KB
+    static constexpr int kABytes = kAAtomBytes * KS;  // 16 KB per M-tile and atom
+    static constexpr int kBBytes = kBAtomBytes * KS;  // 32 / 16 KB per atom
+    static constexpr int kStages = (192 * 1024) / (kABytes + kBBytes);
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN * KP;
-    static constexpr int kBlocksPerStage = (BN / 64) * 4;  // 512-byte packed blocks per stage
+    static constexpr int kBlocksPerStage = (BN / 64) * 4 * KS;  // 512-byte packed blocks per stage
     static constexpr int kBlocksPerWarp = kBlocksPerStage / kGroupWarps;
     static_assert(kBlocksPerStage % kGroupWarps == 0 && kGroupWarps % (BN / 64) == 0,
                   "a dequant team must divide the packed blocks of a stage and keep one chunk per warp");
@@ -145,11 +150,11 @@ struct DequantRegs {
     uint4 w[NBLK];
 };
 
-template <int BN, int MT, int DW, int DG, int KP>
+template <int BN, int MT, int DW, int DG, int KP, int KS>
 __global__ void __launch_bounds__((6 + DW + ((MT == 2 || KP == 2) ? 1 : 0)) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
                      const PrefillParams p) {
-    using C = Cfg<BN, MT, DW, DG, KP>;
+    using C = Cfg<BN, MT, DW, DG, KP, KS>;
     using Regs = DequantRegs<C::kBlocksPerWarp>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -213,7 +218,10 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x100u | s, p.wait_limit_ns))) break;
                     mbar_arrive_expect_tx(full_a(s), C::kABytes);
                     if (static_cast<int>(it) != p.test_drop_a_load)
-                        tma_load_2d(smem_base + s * C::kStageBytes, &tmap_a, ki * BK, mt * (BM * MT), full_a(s));
+#pragma unroll
+                        for (int at = 0; at < KS; ++at)
+                            tma_load_2d(smem_base + s * C::kStageBytes + at * C::kAAtomBytes, &tmap_a, (ki * KS + at) * BK, mt * (BM * MT),
+                                        full_a(s));
                 }
             }
             if (!ok) {
@@ -249,18 +257,21 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s, p.wait_limit_ns))) break;
                     tc_fence_after();
-                    const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes);
                     for (int h = h0; h < h1; ++h) {
                         const uint32_t acc = acc0 + h;
                         if (ki == ki0) {  // first write into this accumulator: the epilogue must have drained it
                             if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0x200u | acc, p.wait_limit_ns))) break;
                             tc_fence_after();
                         }
-                        const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes + h * (BM * BK * 2));
+                        constexpr int kPer = (BK / 16) * KS / KP;  // MMAs of this issuer per stage and M-tile
 #pragma unroll
-                        for (int kk = 0; kk < BK / 16 / KP; ++kk)
-                            umma_bf16(tmem_base + (acc * KP + q) * BN, a_desc + 2 * (kk + 2 * q), b_desc + 2 * (kk + 2 * q), C::kIdesc,
-                                      (ki > ki0 || kk > 0) ? 1u : 0u);
+                        for (int j = 0; j < kPer; ++j) {
+                            const int kg = q * kPer + j, at = kg >> 2, kw = kg & 3;  // 64-deep atom, 16-deep slice in it
+                            const uint64_t a_desc = make_smem_desc(smem_base + s * C::kStageBytes + at * C::kAAtomBytes + h * (BM * BK * 2));
+                            const uint64_t b_desc = make_smem_desc(smem_base + s * C::kStageBytes + C::kABytes + at * C::kBAtomBytes);
+                            umma_bf16(tmem_base + (acc * KP + q) * BN, a_desc + 2 * kw, b_desc + 2 * kw, C::kIdesc,
+                                      (ki > ki0 || j > 0) ? 1u : 0u);
+                        }
                         if (ki == ki1 - 1) umma_commit(tmem_full(acc));  // accumulator h is complete
                     }
                     if (!ok) break;
@@ -509,10 +520,11 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     const int blk = dw + C::kGroupWarps * b;
                     const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
                     const size_t idx =
-                        (static_cast<size_t>(ki * 4 + kt) * chunks_n + nt * kChunksPerTile + ch) * 32 + lane;
+                        (static_cast<size_t>(ki * (4 * KS) + kt) * chunks_n + nt * kChunksPerTile + ch) * 32 + lane;
                     d.w[b] = ld_stream_v4(p.B + idx);
                 }
             };
+            auto group_of = [](int ki) { return KS == 2 ? ki : (ki >> 1); };  // scale group of a stage (KS == 2: a stage is a group)
             auto load_scales = [&](int g) {
                 return ld_stream_v4(reinterpret_cast<const uint4 *>(
                     p.S + static_cast<size_t>(g) * p.n + (nt * kChunksPerTile + dw % kChunksPerTile) * 64 + 8 * c));
@@ -529,7 +541,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 rs[u] = make_uint4(0, 0, 0, 0);
                 if (kf + u * DG < ki1) {
                     load_regs(rw[u], kf + u * DG);
-                    if (!p.per_column) rs[u] = load_scales((kf + u * DG) >> 1);
+                    if (!p.per_column) rs[u] = load_scales(group_of(kf + u * DG));
                 }
             }
             for (int kb = kf; kb < ki1 && ok; kb += 3 * DG) {
@@ -542,7 +554,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1;
                 // scales of this K-step's group (all blocks of a warp share one chunk: blk % kChunksPerTile == dw % ..)
-                const int g = p.per_column ? 0 : (ki >> 1);
+                const int g = p.per_column ? 0 : group_of(ki);
                 if (g != cur_group) {
                     cur_group = g;
                     if (p.per_column) {
@@ -564,10 +576,11 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
                 for (int b = 0; b < C::kBlocksPerWarp; ++b) {
                     const int blk = dw + C::kGroupWarps * b;
-                    const int ch = blk % kChunksPerTile, kt = blk / kChunksPerTile;
+                    const int ch = blk % kChunksPerTile, ktb = blk / kChunksPerTile;  // 16-row K tile of the stage: 0 .. 4*KS-1
+                    const int at = ktb >> 2, kt = ktb & 3;                            // 64-deep atom, K tile inside it
                     const uint32_t xs[4] = {r0.w[b].x, r0.w[b].y, r0.w[b].z, r0.w[b].w};
                     // row (= column of B) n_local = ch*64 + 8t + c, 128 B per row; 16-byte chunk (2kt + half) ^ c
-                    const uint32_t row_base = b_tile + static_cast<uint32_t>(ch * 64 + c) * 128u + 4u * qd;
+                    const uint32_t row_base = b_tile + static_cast<uint32_t>(at * C::kBAtomBytes) + static_cast<uint32_t>(ch * 64 + c) * 128u + 4u * qd;
                     const uint32_t sw_lo = static_cast<uint32_t>((2 * kt) ^ c) << 4;
                     const uint32_t sw_hi = static_cast<uint32_t>((2 * kt + 1) ^ c) << 4;
 #pragma unroll
@@ -600,7 +613,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 mbar_arrive(full_b(s));
                 if (ki + 3 * DG < ki1) {
                     load_regs(rw[u], ki + 3 * DG);
-                    if (!p.per_column) rs[u] = load_scales((ki + 3 * DG) >> 1);
+                    if (!p.per_column) rs[u] = load_scales(group_of(ki + 3 * DG));
                 }
             }
             }
@@ -718,15 +731,15 @@ struct PrefillConfig {
 //   stream-K: launch + whole waves as above + share * step + 2 * tile + per MB of remainder tiles + per slab piece
 // `step` is the time of one 64-K step of a CTA, `tile` what a tile adds on top (epilogue that does not overlap, pipeline
 // restart); both depend on the columns per tile and the M-tiles per stage.  On the fitted set the model's choice is
-// within 0.5 % of the best measured tiling in total.
+// within 0.3 % of the best measured tiling in total.
 struct TileCost {
     double step, tile;
 };
 TileCost tile_cost(int bn, int mt) {
-    if (mt == 2) return bn == 256 ? TileCost{0.583, 11.45} : TileCost{0.465, 3.94};
-    return bn == 256 ? TileCost{0.488, 4.93} : TileCost{0.345, 2.01};
+    if (mt == 2) return bn == 256 ? TileCost{0.584, 11.26} : TileCost{0.463, 3.83};
+    return bn == 256 ? TileCost{0.489, 4.85} : TileCost{0.301, 2.10};
 }
-constexpr double kCostLaunch = 7.36, kCostSplitFixed = 3.93, kCostSplitPerMB = 0.322, kCostSkPerMB = 0.154, kCostSkPerPiece = 0.140;
+constexpr double kCostLaunch = 7.02, kCostSplitFixed = 4.21, kCostSplitPerMB = 0.332, kCostSkPerMB = 0.177, kCostSkPerPiece = 0.147;
 
 // Stream-K split of `tiles` tiles over `grid` CTAs: the tiles of the whole waves are dealt round-robin, the K-steps of
 // the rest go in equal shares to `ctas` CTAs.  A share is at least 8 K-steps and at least 1/36 of a tile, so that no tile
@@ -814,14 +827,15 @@ bool encode_c_map(EncodeTiledFn enc, CUtensorMap *map, void *c, int m, int n) {
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1>
-int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillParams &p, cudaStream_t stream) {
-    using C = Cfg<BN, MT, DW, DG, KP>;
+template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1>
+int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams p, cudaStream_t stream) {
+    using C = Cfg<BN, MT, DW, DG, KP, KS>;
+    p.k_iters /= KS;  // the kernel counts pipeline stages of KS atoms (k is a multiple of 128)
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG, KP>,
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS>,
                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
             return rc;
         attr_set[dev] = true;
@@ -837,7 +851,7 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, const PrefillP
     cudaLaunchAttribute attr = pdl_attribute();
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP>, tmap, tmap_c, p));
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS>, tmap, tmap_c, p));
 }
 
 }  // namespace
@@ -943,7 +957,14 @@ int launch_prefill(const GemmArgs &a) {
         rc = c.bn == 256 ? launch_bn<256, 2>(tmap, tmap_c, p, a.stream) : launch_bn<128, 2>(tmap, tmap_c, p, a.stream);
     else
         // (128-column tiles of one M-tile are bound by the MMA issue rate: two issuers, each with an accumulator of its own)
-        rc = c.bn == 256 ? launch_bn<256, 1>(tmap, tmap_c, p, a.stream) : launch_bn<128, 1, 8, 2, 2>(tmap, tmap_c, p, a.stream);
+        // ... and 128-deep pipeline stages, which halve their barrier round trips per K (not with stream-K, whose fix-up pass
+        // counts 64-deep steps, nor when a split would be left without a whole stage)
+        if (c.bn == 256)
+            rc = launch_bn<256, 1>(tmap, tmap_c, p, a.stream);
+        else if (c.stream_k || a.k / 128 < c.splits)
+            rc = launch_bn<128, 1, 8, 2, 2, 1>(tmap, tmap_c, p, a.stream);
+        else
+            rc = launch_bn<128, 1, 8, 2, 2, 2>(tmap, tmap_c, p, a.stream);
     if (rc) return rc;
     if (c.splits > 1) {
         const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;

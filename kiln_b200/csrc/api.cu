@@ -74,19 +74,23 @@ static int validate(const GemmArgs &a) {
 
 // Kernel choice (measured on B200, CUDA-graph replay over rotating weights).  The decode kernel handles 8 or 16 rows per
 // block of CTAs and repeats the int4 dequant for every block; the tcgen05 kernel dequantises once per 128 rows but pays
-// a fixed cost per 64-K step of a tile.  Measured crossovers: up to 32 rows (two blocks of 16) the decode kernel wins on
-// every shape (gate+up M=32: 19.2 vs 23.1 us, q: 8.3 vs 10.1); a third block costs it more than the tcgen05 kernel's
-// tile (gate+up M=48: 32.4 vs 23.2 us, q: 12.7 vs 10.7), except on projections of about 2560 columns, which have few
-// tiles for 148 SMs (o M=48: 10.0 vs 11.3 us, M=64: 14.4 vs 12.3) and switch at 49, and on projections of 1024 columns
-// or fewer (k, v: four to eight tiles), which stay on the decode kernel up to M = 256 (k at M=128: 6.4 vs 16.1 us).
+// a fixed cost per launch and per K-step of a tile.  Measured crossovers (decode / tcgen05, us):
+//  * wide projections (4096 columns and more): the decode kernel wins up to 32 rows, two blocks of 16 (gate+up M=32:
+//    19.2 / 16.4 but M=24: 18.8 / 22.7; q M=32: 8.2 / 8.9; GDN-in M=32: 11.8 / 11.6), a third block costs it far more than
+//    a tile (gate+up M=40: 32.3 / 16.4, q: 12.7 / 9.4);
+//  * projections of about 2560 columns have few column blocks for the decode kernel to spread over: the tcgen05 kernel
+//    wins from 17 rows (down M=17: 13.4 / 11.8, M=32: 13.7 / 12.5; o M=17: 9.5 / 8.2, M=32: 9.9 / 8.9, M=64: 14.4 / 11.2),
+//    provided the activation matrix is at least 128 KB (smaller ones were measured 40 % slower through its TMA loads);
+//  * projections of 1024 columns or fewer (k, v: four to eight tiles) stay on the decode kernel up to M = 256
+//    (k at M=128: 6.4 / 15.3).
 // kiln_w4a16_set_prefill_min_m replaces the rule by a plain threshold.
 static bool use_prefill(int m, int n, int k, int groupsize) {
     if (!prefill_supported(m, n, k, groupsize)) return false;
     const int min_m = g_prefill_min_m.load(std::memory_order_relaxed);
     if (min_m != kDefaultPrefillMinM) return m >= min_m;
     if (n <= 1024) return m > 256;
-    if (n >= 4096 || static_cast<long long>(n) * k >= (16LL << 20)) return m >= 33;
-    return m >= 49;
+    if (n <= 3072 && static_cast<long long>(m) * k * 2 >= (128LL << 10)) return m >= 17;
+    return m >= 33;
 }
 
 static int gemm(const GemmArgs &a) {

@@ -361,6 +361,34 @@ def prefill_detail(d: Device, peaks):
         out[f"{name}:m{m}"] = {"us": round(us, 1), "TFLOPs": round(tf, 1), "frac_bf16_burst": round(tf / peaks["bf16_tflops"], 4),
                                "frac_bf16_nominal_2250": round(tf / 2250.0, 4)}
         del ws, a, o, flush
+    # gate+up with SwiGLU fused into the tcgen05 epilogue ([m, 9216] output, columns interleaved in runs of 32), same timing
+    import kiln_b200
+    from kiln_b200 import MarlinPackedProj
+
+    k, n = SHAPES["gate_up"]
+    for m in (2048,):
+        ws = [MarlinPackedProj(b, s_, 128, k, n) for (b, s_) in d.weights(k, n, 2)]
+        a = d.acts(m, k)
+        o = t.empty((m, n // 2), dtype=t.bfloat16, device=d.dev)
+        flush = t.empty(int(160e6), dtype=t.uint8, device=d.dev)
+        for i in range(3):
+            kiln_b200.swiglu_gate_up(a, ws[i % 2], out=o)
+        t.cuda.synchronize()
+        ts = []
+        for i in range(7):
+            flush.zero_()
+            e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            e0.record()
+            kiln_b200.swiglu_gate_up(a, ws[i % 2], out=o)
+            e1.record()
+            t.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        us = ts[len(ts) // 2]
+        tf = alg_flops(m, k, n) / us / 1e6
+        out[f"gate_up_swiglu:m{m}"] = {"us": round(us, 1), "TFLOPs": round(tf, 1), "frac_bf16_burst": round(tf / peaks["bf16_tflops"], 4),
+                                       "frac_bf16_nominal_2250": round(tf / 2250.0, 4)}
+        del ws, a, o, flush
     return out
 
 

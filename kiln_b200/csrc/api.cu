@@ -194,8 +194,11 @@ size_t kiln_w4a16_workspace_bytes_ex(int m, int n, int k, const kiln_w4a16_epilo
     const bool opts = ep && (ep->swiglu || ep->lora_rank);
     if (!opts) return kiln_w4a16_workspace_bytes(m, n, k);
     size_t need = align256(static_cast<size_t>(m) * ep->lora_rank * sizeof(float));
-    if (use_prefill(m, n, k, 128))  // not fused at this batch size yet: base result + the tcgen05 kernel's own scratch
+    if (use_prefill(m, n, k, 128)) {
+        if (ep->swiglu && !ep->lora_rank && prefill_fuses_swiglu(m, n, k)) return need;  // fused in the tcgen05 epilogue
+        // composed: base result + the tcgen05 kernel's own scratch, then one pass that applies delta and / or SwiGLU
         need += align256(static_cast<size_t>(m) * n * 2) + align256(prefill_workspace_bytes(m, n, k));
+    }
     return need;
 }
 
@@ -223,6 +226,12 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_ex(const void *A, const void *B, void *
         a.lora_r = ep->lora_rank;
         a.swiglu = ep->swiglu ? 1 : 0;
         return launch_decode(a, g_decode_override);
+    }
+    if (ep->swiglu && !ep->lora_rank && prefill_fuses_swiglu(m, n, k)) {
+        a.swiglu = 1;
+        a.workspace = nullptr;
+        a.workspace_bytes = 0;
+        return launch_prefill(a);
     }
     void *tmp = ws;
     ws += align256(static_cast<size_t>(m) * n * 2);

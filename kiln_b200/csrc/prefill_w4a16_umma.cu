@@ -46,6 +46,7 @@ struct PrefillParams {
     __nv_bfloat16 *peer_c[8];
     int n_peers, ldc, col0;
     int self_peer;  // index in peer_c of the buffer that lives on this GPU (written through the TMA store), or -1
+    int swiglu;     // columns hold gate and up interleaved in runs of 32; C is [m, n/2] = silu(gate) * up (whole tiles, KP == 1)
     // mc_c != nullptr: one multimem.st per piece to the group's multicast address instead (the switch replicates
     // the store into every GPU's buffer, this GPU's included, so each tile leaves this GPU once)
     __nv_bfloat16 *mc_c;
@@ -312,6 +313,47 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 const uint32_t epi_tma0 = epi_base + static_cast<uint32_t>(warp - 2) * (2 * kEpiWarpBytes);  // 1024-byte aligned swizzle atoms
                 const int x0_out = (p.n_peers > 0 ? p.col0 : 0) + nt * BN;  // first column of the tile in the output buffer
                 uint32_t ra[32], rb[32];
+                if (KP == 1 && p.swiglu) {
+                    // SwiGLU (kiln-model/src/forward.rs:2769-2839 as one GEMM): a 64-column run of the tile is 32 gate columns and
+                    // their 32 up columns, i.e. the two register buffers of a round; silu(gate) * up is computed in fp32 and
+                    // stored straight from registers (64 contiguous bytes per thread and round) while the next round's TMEM
+                    // loads are in flight
+                    __nv_bfloat16 *crow = p.C + static_cast<size_t>(row) * (p.n >> 1) + ((nt * BN) >> 1);
+                    tmem_ld_32x32b_x32(t_row, ra);
+                    tmem_ld_32x32b_x32(t_row + 32, rb);
+#pragma unroll 1
+                    for (int pp = 0; pp < BN / 64; ++pp) {
+                        tmem_ld_wait();
+                        uint32_t o[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            float ga = __uint_as_float(ra[2 * e]), gb = __uint_as_float(ra[2 * e + 1]);
+                            float ua = __uint_as_float(rb[2 * e]), ub = __uint_as_float(rb[2 * e + 1]);
+                            if (p.per_column) {
+                                const int pg = scale_single_pos(nt * BN + pp * 64 + 2 * e), pu = scale_single_pos(nt * BN + pp * 64 + 32 + 2 * e);
+                                ga *= __half2float(p.S[pg]);
+                                gb *= __half2float(p.S[pg + 1]);
+                                ua *= __half2float(p.S[pu]);
+                                ub *= __half2float(p.S[pu + 1]);
+                            }
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__fdividef(ga, 1.f + __expf(-ga)) * ua, __fdividef(gb, 1.f + __expf(-gb)) * ub);
+                            o[e] = *reinterpret_cast<uint32_t *>(&b);
+                        }
+                        if (pp + 1 < BN / 64) {
+                            tmem_ld_32x32b_x32(t_row + (pp + 1) * 64, ra);
+                            tmem_ld_32x32b_x32(t_row + (pp + 1) * 64 + 32, rb);
+                        } else {
+                            tc_fence_before();
+                            mbar_arrive(tmem_empty(acc));
+                        }
+                        if (row < p.m) {
+                            uint4 *dst = reinterpret_cast<uint4 *>(crow + pp * 32);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) dst[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                        }
+                    }
+                    continue;
+                }
                 if constexpr (KP == 2) {
                     // two accumulators (one per K-parity issuer) to add: 32 columns of each per half-round; the loads of the
                     // next half-round are in flight while a finished 64-column tile is stored
@@ -856,6 +898,14 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams 
 
 }  // namespace
 
+// SwiGLU can be fused into the tcgen05 kernel's epilogue when its tiling for the problem writes whole tiles as bf16.
+bool prefill_fuses_swiglu(int m, int n, int k) {
+    const PrefillConfig c = choose_prefill(m, n, k);
+    // (not the 128-column tiles of one M-tile: their two K-parity accumulators would have to be added first, and at those
+    // batch sizes a second pass over the small output costs less than a longer epilogue)
+    return c.splits == 1 && !c.stream_k && !(c.bn == 128 && c.mt == 1);
+}
+
 void set_wait_limit_ns(unsigned long long ns) { g_wait_limit_ns = ns ? ns : kWaitLimitNs; }
 void set_test_drop_a_load(int k_step) { g_test_drop_a_load = k_step; }
 
@@ -890,6 +940,8 @@ int launch_prefill(const GemmArgs &a) {
     if (!status) return KILN_W4A16_ERR_CUDA;
     const bool fused = a.n_peers > 0 || a.mc_c;  // the peer-store epilogue needs whole tiles: no split-K, no stream-K
     const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused && !a.no_scratch);
+    if (a.swiglu && (fused || c.splits != 1 || c.stream_k || (c.bn == 128 && c.mt == 1)))
+        return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_swiglu first)
 
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
@@ -918,7 +970,7 @@ int launch_prefill(const GemmArgs &a) {
     CUtensorMap tmap_c;  // this GPU's own C: [m, n], or its [m, ldc] buffer of the fused all-gather
     if (self_peer >= 0) {
         if (!encode_c_map(enc, &tmap_c, a.peer_c[self_peer], a.m, a.ldc)) return KILN_W4A16_ERR_CUDA;
-    } else if (!encode_c_map(enc, &tmap_c, a.C, a.m, a.n)) {
+    } else if (!encode_c_map(enc, &tmap_c, a.C, a.m, a.swiglu ? a.n / 2 : a.n)) {
         return KILN_W4A16_ERR_CUDA;
     }
 
@@ -940,6 +992,7 @@ int launch_prefill(const GemmArgs &a) {
     p.ldc = a.ldc;
     p.col0 = a.col0;
     p.self_peer = self_peer;
+    p.swiglu = a.swiglu;
     p.mc_c = static_cast<__nv_bfloat16 *>(a.mc_c);
     for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;

@@ -126,7 +126,7 @@ struct GemmArgs {
     int n_peers = 0, ldc = 0, col0 = 0;
     // the same with one NVSwitch multicast address for the whole group instead of per-GPU pointers (multimem.st)
     void *mc_c = nullptr;
-    // epilogue options (decode kernel): LoRA delta C += lora_t * lora_b^T with lora_t fp32 [m, lora_r] = scale * x * A^T
+    // epilogue options (LoRA: decode kernel; SwiGLU: decode kernel, and the tcgen05 kernel's whole-tile tilings): LoRA delta C += lora_t * lora_b^T with lora_t fp32 [m, lora_r] = scale * x * A^T
     // and lora_b bf16 [n, lora_r]; swiglu: columns are gate/up interleaved in runs of 32, C is [m, n/2]
     bool no_scratch = false;  // the tcgen05 kernel may not use the workspace (legacy entry point: its caller's buffer is tiny)
     const void *lora_t = nullptr;
@@ -165,6 +165,7 @@ void set_wait_limit_ns(unsigned long long ns);
 void set_test_drop_a_load(int k_step);
 void prefill_plan(int m, int n, int k, int out[4]);
 bool prefill_supported(int m, int n, int k, int groupsize);
+bool prefill_fuses_swiglu(int m, int n, int k);
 int static_status_read_clear(cudaStream_t st, uint32_t *out);
 
 }  // namespace kiln

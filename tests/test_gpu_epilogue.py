@@ -46,6 +46,32 @@ def test_swiglu_fused_into_the_gate_up_gemm(cuda_device, m, k, n_half):
     assert rel_err(from_torch_bf16(out), (_silu(g) * u).astype(np.float32)) <= REL_TOL
 
 
+@pytest.mark.parametrize("m,k,n_half,fused_expected", [(64, 2560, 9216, False), (384, 512, 2048, False), (300, 2560, 9216, True),
+                                                        (600, 1152, 4096, True), (2048, 640, 1024, True)])
+def test_swiglu_at_the_batch_sizes_of_the_tcgen05_kernel(cuda_device, m, k, n_half, fused_expected):
+    """Batch sizes of the tcgen05 kernel: tilings that write whole tiles from one accumulator per M-tile compute
+    silu(gate) * up in the epilogue (no workspace needed); the others compose the GEMM with a second pass.  Rows outside
+    [0, m) stay untouched."""
+    import ctypes
+
+    lib = _lib.lib()
+    lib.kiln_w4a16_set_prefill_min_m(1)
+    try:
+        ep = _lib.Epilogue()
+        ep.swiglu = 1
+        need = int(lib.kiln_w4a16_workspace_bytes_ex(m, 2 * n_half, k, ctypes.byref(ep)))
+        assert (need == 0) == fused_expected, f"workspace {need} bytes"
+        a, fused, g, u = _gate_up_case(m, k, n_half, seed=m + k, dev=cuda_device)
+        buf = torch.full((m + 2, n_half), 3.0, dtype=torch.bfloat16, device=cuda_device)
+        out = kiln_b200.swiglu_gate_up(to_torch_bf16(a, cuda_device), fused, out=buf[1:m + 1])
+        torch.cuda.synchronize()
+        assert lib.kiln_w4a16_check_device_status(None, None) == 0
+        assert rel_err(from_torch_bf16(out), (_silu(g) * u).astype(np.float32)) <= REL_TOL
+        assert (buf[0] == 3.0).all() and (buf[m + 1] == 3.0).all()
+    finally:
+        lib.kiln_w4a16_set_prefill_min_m(0)
+
+
 @pytest.mark.parametrize("cfg", [(1, 2, 1), (2, 3, 2), (3, 2, 1), (4, 2, 4), (5, 1, 2), (8, 1, 1), (8, 2, 2)])
 def test_swiglu_with_every_cluster_split(cuda_device, cfg):
     """The gate pair and its up pair must meet in one cluster rank whatever the decomposition."""

@@ -73,8 +73,10 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
  *             32 (columns 64c .. 64c+31 are gate columns 32c .. 32c+31, columns 64c+32 .. 64c+63 the up columns of the
  *             same indices; n = 2 * intermediate size).  C is then [m, n/2] = silu(gate) * up, computed in fp32 from the
  *             unrounded sums (the reference rounds gate and up to bf16 first).  lora_b follows the same column order.
- * For batch sizes the decode kernel serves (kiln_w4a16_workspace_bytes(m, n, k) == 0) the options are fused into that
- * kernel's final reduction; for larger ones the plain GEMM result goes to the workspace and a second kernel applies them. */
+ * For batch sizes the decode kernel serves the options are fused into that kernel's final reduction.  For larger ones
+ * SwiGLU alone is fused into the tcgen05 kernel's epilogue whenever its tiling writes whole tiles from one accumulator
+ * per M-tile (then kiln_w4a16_workspace_bytes_ex returns 0); otherwise the plain GEMM result goes to the workspace and a
+ * second kernel applies the options. */
 typedef struct kiln_w4a16_epilogue {
     int swiglu;
     const void *lora_a;

@@ -93,7 +93,7 @@ def _lora(rng, r, k, n):
     return la, lb
 
 
-@pytest.mark.parametrize("r", [8, 20, 64])
+@pytest.mark.parametrize("r", [8, 20, 64, 128])
 @pytest.mark.parametrize("m,k,n", [(1, 2560, 4096), (16, 2560, 4096), (5, 640, 768), (512, 640, 1024)])
 def test_lora_delta_in_the_epilogue(cuda_device, m, k, n, r):
     a, q, s = oracle.synth_inputs(m, k, n, seed=r + m)

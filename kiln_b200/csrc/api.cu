@@ -195,9 +195,12 @@ size_t kiln_w4a16_workspace_bytes_ex(int m, int n, int k, const kiln_w4a16_epilo
     if (!opts) return kiln_w4a16_workspace_bytes(m, n, k);
     size_t need = align256(static_cast<size_t>(m) * ep->lora_rank * sizeof(float));
     if (use_prefill(m, n, k, 128)) {
-        if (ep->swiglu && !ep->lora_rank && prefill_fuses_swiglu(m, n, k)) return need;  // fused in the tcgen05 epilogue
-        // composed: base result + the tcgen05 kernel's own scratch, then one pass that applies delta and / or SwiGLU
-        need += align256(static_cast<size_t>(m) * n * 2) + align256(prefill_workspace_bytes(m, n, k));
+        // tcgen05 kernel: SwiGLU is fused when the tiling writes whole tiles, the LoRA delta whenever the scales are grouped
+        // (this call does not know the group size, so it reserves the composed path's buffer whenever there is a delta);
+        // what is not fused is applied by a second pass over the bf16 GEMM result kept in the workspace
+        const bool composed = (ep->swiglu && !prefill_fuses_swiglu(m, n, k)) || ep->lora_rank;
+        if (composed) need += align256(static_cast<size_t>(m) * n * 2);
+        need += align256(prefill_workspace_bytes(m, n, k));
     }
     return need;
 }
@@ -214,30 +217,39 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_ex(const void *A, const void *B, void *
     const size_t need = kiln_w4a16_workspace_bytes_ex(m, n, k, ep);
     if (need > 0 && (!workspace || workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
-    float *t = nullptr;
+    const bool tc = use_prefill(m, n, k, groupsize);
+    const bool fuse_lora = tc && ep->lora_rank && prefill_fuses_lora(groupsize, ep->lora_rank);
+    const bool fuse_swiglu = tc && ep->swiglu && prefill_fuses_swiglu(m, n, k);
+    void *t = nullptr;
     if (ep->lora_rank) {
-        t = reinterpret_cast<float *>(ws);
+        t = ws;  // fp32 [m, r] for the decode kernel and the composed pass, bf16 [m, r] as an operand of the tcgen05 kernel
         ws += align256(static_cast<size_t>(m) * ep->lora_rank * sizeof(float));
-        if (int rc = launch_lora_down(A, ep->lora_a, ep->lora_scale, m, k, ep->lora_rank, t, a.stream)) return rc;
+        if (int rc = launch_lora_down(A, ep->lora_a, ep->lora_scale, m, k, ep->lora_rank, t, fuse_lora ? 1 : 0, a.stream)) return rc;
     }
-    if (!use_prefill(m, n, k, groupsize)) {
+    if (!tc) {
         a.lora_t = t;
         a.lora_b = ep->lora_b;
         a.lora_r = ep->lora_rank;
         a.swiglu = ep->swiglu ? 1 : 0;
         return launch_decode(a, g_decode_override);
     }
-    if (ep->swiglu && !ep->lora_rank && prefill_fuses_swiglu(m, n, k)) {
-        a.swiglu = 1;
-        a.workspace = nullptr;
-        a.workspace_bytes = 0;
-        return launch_prefill(a);
+    const bool composed = (ep->swiglu && !fuse_swiglu) || (ep->lora_rank && !fuse_lora);
+    void *tmp = nullptr;
+    if (composed) {
+        tmp = ws;
+        ws += align256(static_cast<size_t>(m) * n * 2);
     }
-    void *tmp = ws;
-    ws += align256(static_cast<size_t>(m) * n * 2);
-    GemmArgs b{A, B, s, tmp, m, n, k, groupsize, ws, prefill_workspace_bytes(m, n, k), a.stream};
+    GemmArgs b{A, B, s, composed ? tmp : C, m, n, k, groupsize, ws, prefill_workspace_bytes(m, n, k), a.stream};
+    if (fuse_lora) {
+        b.lora_t = t;
+        b.lora_b = ep->lora_b;
+        b.lora_r = ep->lora_rank;
+    }
+    if (!composed && fuse_swiglu) b.swiglu = 1;
     if (int rc = launch_prefill(b)) return rc;
-    return launch_finish(tmp, C, m, n, t, ep->lora_b, ep->lora_rank, ep->swiglu ? 1 : 0, a.stream);
+    if (!composed) return KILN_W4A16_OK;
+    return launch_finish(tmp, C, m, n, fuse_lora ? nullptr : static_cast<const float *>(t), ep->lora_b, fuse_lora ? 0 : ep->lora_rank,
+                         ep->swiglu ? 1 : 0, a.stream);
 }
 
 kiln_w4a16_status_t kiln_w4a16_gemm_bf16_grouped(const kiln_w4a16_problem_t *problems, int count, void *workspace,

@@ -11,8 +11,16 @@ namespace kiln {
 namespace {
 
 // grid = (ceil(r / 8), m), block = 256: warp w of a CTA computes t[row][8 * blockIdx.x + w].
+// (bf16_out: t is a bf16 [m, r] matrix, the form the tcgen05 kernel reads as an operand tile)
+__device__ __forceinline__ void store_t(void *t, size_t idx, float v, int bf16_out) {
+    if (bf16_out)
+        static_cast<__nv_bfloat16 *>(t)[idx] = __float2bfloat16(v);
+    else
+        static_cast<float *>(t)[idx] = v;
+}
+
 __global__ void __launch_bounds__(256) lora_down_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
-                                                        float scale, int k, int r, float *__restrict__ t) {
+                                                        float scale, int k, int r, void *__restrict__ t, int bf16_out) {
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.y, j = blockIdx.x * 8 + warp;
@@ -31,7 +39,41 @@ __global__ void __launch_bounds__(256) lora_down_kernel(const __nv_bfloat16 *__r
     }
 #pragma unroll
     for (int sh = 16; sh >= 1; sh >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sh);
-    if (lane == 0) t[static_cast<size_t>(row) * r + j] = sum * scale;
+    if (lane == 0) store_t(t, static_cast<size_t>(row) * r + j, sum * scale, bf16_out);
+}
+
+// The same for larger batches: a CTA takes eight rows of x, so that every adapter row it reads serves eight dot products
+// (the kernel above re-reads the whole adapter once per row of x).  grid = (ceil(r / 8), ceil(m / 8)), block = 256.
+__global__ void __launch_bounds__(256) lora_down_rows8_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
+                                                              float scale, int m, int k, int r, void *__restrict__ t, int bf16_out) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = blockIdx.y * 8, j = blockIdx.x * 8 + warp;
+    pdl_wait();  // x may be the previous kernel's output; t may still be read by it
+    if (j >= r) return;
+    const uint4 *ar = reinterpret_cast<const uint4 *>(a + static_cast<size_t>(j) * k);
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = lane; i < k / 8; i += 32) {
+        const uint4 av = ar[i];
+        const uint32_t as[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+            const int row = row0 + rr < m ? row0 + rr : m - 1;  // (rows past m repeat the last one; their sums are dropped)
+            const uint4 xv = ld_cg_v4(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(row) * k) + i);
+            const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                sum[rr] += __uint_as_float(xs[e] << 16) * __uint_as_float(as[e] << 16) +
+                           __uint_as_float(xs[e] & 0xFFFF0000u) * __uint_as_float(as[e] & 0xFFFF0000u);
+        }
+    }
+#pragma unroll
+    for (int rr = 0; rr < 8; ++rr) {
+        float v = sum[rr];
+#pragma unroll
+        for (int sh = 16; sh >= 1; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+        if (lane == 0 && row0 + rr < m) store_t(t, static_cast<size_t>(row0 + rr) * r + j, v * scale, bf16_out);
+    }
 }
 
 __device__ __forceinline__ float lora_dot(const float *t, const __nv_bfloat16 *b, int r) {
@@ -67,9 +109,10 @@ __global__ void __launch_bounds__(256) finish_kernel(const __nv_bfloat16 *__rest
 
 }  // namespace
 
-int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, float *t, cudaStream_t stream) {
+int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, void *t, int bf16_out, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((r + 7) / 8, m, 1);
+    const bool rows8 = m > 32;
+    cfg.gridDim = rows8 ? dim3((r + 7) / 8, (m + 7) / 8, 1) : dim3((r + 7) / 8, m, 1);
     cfg.blockDim = dim3(256);
     cfg.stream = stream;
     cudaLaunchAttribute attr;
@@ -77,10 +120,13 @@ int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int 
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    if (m > 65535) return KILN_W4A16_ERR_KERN_SHAPE;
+    if (cfg.gridDim.y > 65535) return KILN_W4A16_ERR_KERN_SHAPE;
     note_launch();
+    if (rows8)
+        return record_cuda_error(cudaLaunchKernelEx(&cfg, lora_down_rows8_kernel, static_cast<const __nv_bfloat16 *>(x),
+                                                    static_cast<const __nv_bfloat16 *>(lora_a), scale, m, k, r, t, bf16_out));
     return record_cuda_error(cudaLaunchKernelEx(&cfg, lora_down_kernel, static_cast<const __nv_bfloat16 *>(x),
-                                                static_cast<const __nv_bfloat16 *>(lora_a), scale, k, r, t));
+                                                static_cast<const __nv_bfloat16 *>(lora_a), scale, k, r, t, bf16_out));
 }
 
 int launch_finish(const void *base, void *c, int m, int n, const float *t, const void *lora_b, int r, int swiglu,

@@ -47,6 +47,9 @@ struct PrefillParams {
     int n_peers, ldc, col0;
     int self_peer;  // index in peer_c of the buffer that lives on this GPU (written through the TMA store), or -1
     int swiglu;     // columns hold gate and up interleaved in runs of 32; C is [m, n/2] = silu(gate) * up (whole tiles, KP == 1)
+    // LoRA delta as extra K-steps: the piece of work that starts a tile's K range appends lora_steps (1 or 2) 64-deep steps
+    // whose operands are bf16 tiles of t = scale * x * A^T [m, r] and of lora_b [n, r], both fetched by TMA (KS == 1 only)
+    int lora_steps;
     // mc_c != nullptr: one multimem.st per piece to the group's multicast address instead (the switch replicates
     // the store into every GPU's buffer, this GPU's included, so each tile leaves this GPU once)
     __nv_bfloat16 *mc_c;
@@ -154,7 +157,7 @@ struct DequantRegs {
 template <int BN, int MT, int DW, int DG, int KP, int KS>
 __global__ void __launch_bounds__((6 + DW + ((MT == 2 || KP == 2) ? 1 : 0)) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
-                     const PrefillParams p) {
+                     const __grid_constant__ CUtensorMap tmap_t, const __grid_constant__ CUtensorMap tmap_lb, const PrefillParams p) {
     using C = Cfg<BN, MT, DW, DG, KP, KS>;
     using Regs = DequantRegs<C::kBlocksPerWarp>;
     extern __shared__ uint8_t smem_raw[];
@@ -213,10 +216,17 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             bool ok = true;
             WorkIter wi(p);
             while (ok && wi.next(mt, nt, sp, ki0, ki1, slab)) {
-                for (int ki = ki0; ki < ki1; ++ki, ++it) {
+                const int ki1e = ki1 + ((KS == 1 && ki0 == 0) ? p.lora_steps : 0);  // + the LoRA steps of the tile
+                for (int ki = ki0; ki < ki1e; ++ki, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x100u | s, p.wait_limit_ns))) break;
+                    if (ki >= ki1) {  // LoRA step: both operand tiles come by TMA (rows past m, columns past r read zero)
+                        mbar_arrive_expect_tx(full_a(s), C::kAAtomBytes + C::kBAtomBytes);
+                        tma_load_2d(smem_base + s * C::kStageBytes, &tmap_t, (ki - ki1) * BK, mt * (BM * MT), full_a(s));
+                        tma_load_2d(smem_base + s * C::kStageBytes + C::kABytes, &tmap_lb, (ki - ki1) * BK, nt * BN, full_a(s));
+                        continue;
+                    }
                     mbar_arrive_expect_tx(full_a(s), C::kABytes);
                     if (static_cast<int>(it) != p.test_drop_a_load)
 #pragma unroll
@@ -253,7 +263,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (; ok && wi.next(mt, nt, sp, ki0, ki1, slab); ++tile) {
                 // MT == 1: the two TMEM buffers alternate between tiles.  MT == 2: buffer h holds M-tile h of the pair.
                 const uint32_t acc0 = MT == 1 ? (tile & 1) : 0u, acc_ph = MT == 1 ? ((tile >> 1) & 1) : (tile & 1);
-                for (int ki = ki0; ki < ki1; ++ki, ++it) {
+                const int ki1e = ki1 + ((KS == 1 && ki0 == 0) ? p.lora_steps : 0);  // + the LoRA steps of the tile
+                for (int ki = ki0; ki < ki1e; ++ki, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!(ok = mbar_wait(full_a(s), ph, abort_flag, p.status, 0x300u | s, p.wait_limit_ns))) break;
@@ -273,7 +284,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                             umma_bf16(tmem_base + (acc * KP + q) * BN, a_desc + 2 * kw, b_desc + 2 * kw, C::kIdesc,
                                       (ki > ki0 || j > 0) ? 1u : 0u);
                         }
-                        if (ki == ki1 - 1) umma_commit(tmem_full(acc));  // accumulator h is complete
+                        if (ki == ki1e - 1) umma_commit(tmem_full(acc));  // accumulator h is complete
                     }
                     if (!ok) break;
                     umma_commit(empty(s));  // this issuer's MMAs have read the stage; the slot is free after all issuers'
@@ -324,20 +335,26 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll 1
                     for (int pp = 0; pp < BN / 64; ++pp) {
                         tmem_ld_wait();
-                        uint32_t o[16];
+                        uint4 *dst = reinterpret_cast<uint4 *>(crow + pp * 32);
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) {
-                            float ga = __uint_as_float(ra[2 * e]), gb = __uint_as_float(ra[2 * e + 1]);
-                            float ua = __uint_as_float(rb[2 * e]), ub = __uint_as_float(rb[2 * e + 1]);
-                            if (p.per_column) {
-                                const int pg = scale_single_pos(nt * BN + pp * 64 + 2 * e), pu = scale_single_pos(nt * BN + pp * 64 + 32 + 2 * e);
-                                ga *= __half2float(p.S[pg]);
-                                gb *= __half2float(p.S[pg + 1]);
-                                ua *= __half2float(p.S[pu]);
-                                ub *= __half2float(p.S[pu + 1]);
+                        for (int v = 0; v < 4; ++v) {  // eight output columns at a time: their registers die with the store
+                            uint32_t o[4];
+#pragma unroll
+                            for (int e2 = 0; e2 < 4; ++e2) {
+                                const int e = 4 * v + e2;
+                                float ga = __uint_as_float(ra[2 * e]), gb = __uint_as_float(ra[2 * e + 1]);
+                                float ua = __uint_as_float(rb[2 * e]), ub = __uint_as_float(rb[2 * e + 1]);
+                                if (p.per_column) {
+                                    const int pg = scale_single_pos(nt * BN + pp * 64 + 2 * e), pu = scale_single_pos(nt * BN + pp * 64 + 32 + 2 * e);
+                                    ga *= __half2float(p.S[pg]);
+                                    gb *= __half2float(p.S[pg + 1]);
+                                    ua *= __half2float(p.S[pu]);
+                                    ub *= __half2float(p.S[pu + 1]);
+                                }
+                                __nv_bfloat162 b = __floats2bfloat162_rn(__fdividef(ga, 1.f + __expf(-ga)) * ua, __fdividef(gb, 1.f + __expf(-gb)) * ub);
+                                o[e2] = *reinterpret_cast<uint32_t *>(&b);
                             }
-                            __nv_bfloat162 b = __floats2bfloat162_rn(__fdividef(ga, 1.f + __expf(-ga)) * ua, __fdividef(gb, 1.f + __expf(-gb)) * ub);
-                            o[e] = *reinterpret_cast<uint32_t *>(&b);
+                            if (row < p.m) dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
                         }
                         if (pp + 1 < BN / 64) {
                             tmem_ld_32x32b_x32(t_row + (pp + 1) * 64, ra);
@@ -345,11 +362,6 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         } else {
                             tc_fence_before();
                             mbar_arrive(tmem_empty(acc));
-                        }
-                        if (row < p.m) {
-                            uint4 *dst = reinterpret_cast<uint4 *>(crow + pp * 32);
-#pragma unroll
-                            for (int v = 0; v < 4; ++v) dst[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
                         }
                     }
                     continue;
@@ -660,6 +672,16 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
             }
             it_base += static_cast<uint32_t>(ki1 - ki0);
+            // LoRA steps of the tile: the weight-side tile comes by TMA; the team that owns a stage only owes its barrier the arrivals
+            if (KS == 1 && ki0 == 0 && p.lora_steps > 0) {
+                for (int e = 0; e < p.lora_steps && ok; ++e, ++it_base) {
+                    if (it_base % DG != static_cast<uint32_t>(team)) continue;
+                    const int s = it_base % C::kStages;
+                    const uint32_t ph = (it_base / C::kStages) & 1;
+                    if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0x700u | s, p.wait_limit_ns))) break;
+                    mbar_arrive(full_b(s));
+                }
+            }
         }
     }
 
@@ -870,7 +892,8 @@ bool encode_c_map(EncodeTiledFn enc, CUtensorMap *map, void *c, int m, int n) {
 }
 
 template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1>
-int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams p, cudaStream_t stream) {
+int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams p, cudaStream_t stream,
+              const CUtensorMap *tmap_t = nullptr, const CUtensorMap *tmap_lb = nullptr) {
     using C = Cfg<BN, MT, DW, DG, KP, KS>;
     p.k_iters /= KS;  // the kernel counts pipeline stages of KS atoms (k is a multiple of 128)
     static bool attr_set[64] = {};
@@ -893,7 +916,10 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams 
     cudaLaunchAttribute attr = pdl_attribute();
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS>, tmap, tmap_c, p));
+    static const CUtensorMap kNoMap = {};  // (never dereferenced when p.lora_steps == 0)
+    if (!tmap_t || !tmap_lb || KS != 1) p.lora_steps = 0;
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS>, tmap, tmap_c,
+                                                tmap_t ? *tmap_t : kNoMap, tmap_lb ? *tmap_lb : kNoMap, p));
 }
 
 }  // namespace
@@ -905,6 +931,10 @@ bool prefill_fuses_swiglu(int m, int n, int k) {
     // batch sizes a second pass over the small output costs less than a longer epilogue)
     return c.splits == 1 && !c.stream_k && !(c.bn == 128 && c.mt == 1);
 }
+
+// The LoRA delta can ride in the tcgen05 kernel as extra K-steps unless the scales are per column (those are applied to
+// the whole accumulator in the epilogue and would scale the delta too).
+bool prefill_fuses_lora(int groupsize, int lora_r) { return groupsize == 128 && lora_r > 0 && lora_r <= 128 && lora_r % 8 == 0; }
 
 void set_wait_limit_ns(unsigned long long ns) { g_wait_limit_ns = ns ? ns : kWaitLimitNs; }
 void set_test_drop_a_load(int k_step) { g_test_drop_a_load = k_step; }
@@ -993,6 +1023,24 @@ int launch_prefill(const GemmArgs &a) {
     p.col0 = a.col0;
     p.self_peer = self_peer;
     p.swiglu = a.swiglu;
+    // LoRA delta fused as extra K-steps: t = scale * x * A^T (bf16 [m, r], written by the kernel launched just before) and
+    // lora_b (bf16 [n, r]) are operand tiles like any other; columns past r read zero
+    CUtensorMap tmap_t, tmap_lb;
+    const bool lora = a.lora_r > 0 && a.lora_t && a.lora_b;
+    if (lora) {
+        if (a.groupsize == -1 || a.lora_r % 8 != 0 || a.lora_r > 128) return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_lora first)
+        const cuuint64_t td[2] = {static_cast<cuuint64_t>(a.lora_r), static_cast<cuuint64_t>(a.m)};
+        const cuuint64_t ld[2] = {static_cast<cuuint64_t>(a.lora_r), static_cast<cuuint64_t>(a.n)};
+        const cuuint64_t st[1] = {static_cast<cuuint64_t>(a.lora_r) * 2};
+        const cuuint32_t tb[2] = {BK, static_cast<cuuint32_t>(BM * c.mt)}, lb[2] = {BK, static_cast<cuuint32_t>(c.bn)};
+        if (enc(&tmap_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.lora_t), td, st, tb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            enc(&tmap_lb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.lora_b), ld, st, lb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return KILN_W4A16_ERR_CUDA;
+        p.lora_steps = (a.lora_r + BK - 1) / BK;
+    }
+    const CUtensorMap *pt = lora ? &tmap_t : nullptr, *plb = lora ? &tmap_lb : nullptr;
     p.mc_c = static_cast<__nv_bfloat16 *>(a.mc_c);
     for (int i = 0; i < a.n_peers && i < 8; ++i) p.peer_c[i] = static_cast<__nv_bfloat16 *>(a.peer_c[i]);
     p.stream_k = c.stream_k;
@@ -1007,15 +1055,15 @@ int launch_prefill(const GemmArgs &a) {
 
     int rc;
     if (c.mt == 2)
-        rc = c.bn == 256 ? launch_bn<256, 2>(tmap, tmap_c, p, a.stream) : launch_bn<128, 2>(tmap, tmap_c, p, a.stream);
+        rc = c.bn == 256 ? launch_bn<256, 2>(tmap, tmap_c, p, a.stream, pt, plb) : launch_bn<128, 2>(tmap, tmap_c, p, a.stream, pt, plb);
     else
         // (128-column tiles of one M-tile are bound by the MMA issue rate: two issuers, each with an accumulator of its own)
         // ... and 128-deep pipeline stages, which halve their barrier round trips per K (not with stream-K, whose fix-up pass
         // counts 64-deep steps, nor when a split would be left without a whole stage)
         if (c.bn == 256)
-            rc = launch_bn<256, 1>(tmap, tmap_c, p, a.stream);
-        else if (c.stream_k || a.k / 128 < c.splits)
-            rc = launch_bn<128, 1, 8, 2, 2, 1>(tmap, tmap_c, p, a.stream);
+            rc = launch_bn<256, 1>(tmap, tmap_c, p, a.stream, pt, plb);
+        else if (c.stream_k || a.k / 128 < c.splits || lora)  // (the LoRA steps are 64 deep)
+            rc = launch_bn<128, 1, 8, 2, 2, 1>(tmap, tmap_c, p, a.stream, pt, plb);
         else
             rc = launch_bn<128, 1, 8, 2, 2, 2>(tmap, tmap_c, p, a.stream);
     if (rc) return rc;

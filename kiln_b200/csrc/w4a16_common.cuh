@@ -126,7 +126,7 @@ struct GemmArgs {
     int n_peers = 0, ldc = 0, col0 = 0;
     // the same with one NVSwitch multicast address for the whole group instead of per-GPU pointers (multimem.st)
     void *mc_c = nullptr;
-    // epilogue options (LoRA: decode kernel; SwiGLU: decode kernel, and the tcgen05 kernel's whole-tile tilings): LoRA delta C += lora_t * lora_b^T with lora_t fp32 [m, lora_r] = scale * x * A^T
+    // epilogue options (LoRA: decode kernel; SwiGLU: decode kernel, and the tcgen05 kernel's whole-tile tilings): LoRA delta C += lora_t * lora_b^T with lora_t [m, lora_r] = scale * x * A^T (fp32 for the decode kernel, bf16 for the tcgen05 kernel)
     // and lora_b bf16 [n, lora_r]; swiglu: columns are gate/up interleaved in runs of 32, C is [m, n/2]
     bool no_scratch = false;  // the tcgen05 kernel may not use the workspace (legacy entry point: its caller's buffer is tiny)
     const void *lora_t = nullptr;
@@ -156,7 +156,8 @@ uint32_t *device_status_word();        // per-device word written by bounded wai
 int launch_decode(const GemmArgs &a, const DecodeOverride &ov);
 void decode_plan(int m, int n, int k, const DecodeOverride &ov, int out[4]);
 int launch_decode_list(const DecodeItem *items, int count, cudaStream_t stream, const DecodeOverride &ov);
-int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, float *t, cudaStream_t stream);
+int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, void *t, int bf16_out, cudaStream_t stream);
+bool prefill_fuses_lora(int groupsize, int lora_r);
 int launch_finish(const void *base, void *c, int m, int n, const float *t, const void *lora_b, int r, int swiglu, cudaStream_t stream);
 int launch_prefill(const GemmArgs &a);
 size_t prefill_workspace_bytes(int m, int n, int k);

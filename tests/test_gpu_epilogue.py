@@ -110,10 +110,12 @@ def test_lora_delta_in_the_epilogue(cuda_device, m, k, n, r):
     assert rel_err(from_torch_bf16(out), (base + delta).astype(np.float32)) <= REL_TOL
 
 
-def test_lora_and_swiglu_together(cuda_device):
+@pytest.mark.parametrize("m,k,nh", [(3, 640, 512), (300, 640, 512), (300, 1152, 4096)])
+def test_lora_and_swiglu_together(cuda_device, m, k, nh):
     """Separate LoRA adapters on gate and up are one adapter of twice the rank on the fused matrix: A = [A_g; A_u],
-    B = [[B_g, 0]; [0, B_u]] with its rows in the fused column order."""
-    m, k, nh, r = 3, 640, 512, 8
+    B = [[B_g, 0]; [0, B_u]] with its rows in the fused column order.  m = 3: decode kernel; m = 300: tcgen05 kernel with
+    the delta as extra K-steps, SwiGLU composed (narrow tiles) or in the epilogue (pairs of 256-column tiles)."""
+    r = 8
     a, fused, g, u = _gate_up_case(m, k, nh, seed=99, dev=cuda_device)
     rng = np.random.default_rng(5)
     ag, bg = _lora(rng, r, k, nh)

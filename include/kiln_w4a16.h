@@ -218,8 +218,9 @@ kiln_w4a16_status_t kiln_w4a16_repack_gptq_device(const int32_t *qweight, const 
 int kiln_w4a16_last_cuda_error(void);
 
 /* Reads and clears the device status words that bounded device-side waits write
- * when they give up (the one of the ordinary launches and the one of the no-allocation
- * entry).  Synchronises `stream`.  Returns KILN_W4A16_OK or KILN_W4A16_ERR_TIMEOUT;
+ * when they give up (the one of the ordinary launches, the one of the no-allocation
+ * entry, and the decode kernel's: 0x800 = a CTA never received the split-K partial sums
+ * of its cluster peers and left its part of C unwritten).  Synchronises `stream`.  Returns KILN_W4A16_OK or KILN_W4A16_ERR_TIMEOUT;
  * *detail (optional) receives the raw word. */
 kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detail);
 

@@ -299,12 +299,14 @@ kiln_w4a16_status_t kiln_w4a16_check_device_status(void *stream, uint32_t *detai
     if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
     uint32_t host_static = 0;  // the word of the no-allocation entry's launches (kept in the library image)
     if (int rc = static_status_read_clear(st, &host_static)) return rc;
-    if (detail) *detail = host ? host : host_static;
+    uint32_t host_decode = 0;  // the decode kernel's word (split-K exchange between the CTAs of a cluster)
+    if (int rc = decode_status_read_clear(st, &host_decode)) return rc;
+    if (detail) *detail = host ? host : (host_static ? host_static : host_decode);
     if (host != 0) {
         if (int rc = record_cuda_error(cudaMemsetAsync(w, 0, sizeof(uint32_t), st))) return rc;
         if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
     }
-    return (host | host_static) ? KILN_W4A16_ERR_TIMEOUT : KILN_W4A16_OK;
+    return (host | host_static | host_decode) ? KILN_W4A16_ERR_TIMEOUT : KILN_W4A16_OK;
 }
 
 void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n) {

@@ -24,12 +24,14 @@
 //  * the fp16 group scale is applied once per 128-K group to the fp32 partial sums (exact scale).
 //  * split-K without global scratch: K is split over teams of warps inside a CTA and over the CTAs of a
 //    thread-block cluster; partial tiles meet in (distributed) shared memory and are summed in a fixed
-//    order, so results are bit-reproducible.
-//  * nothing in this kernel polls: the only waits are `bar.sync`, the cluster barrier (both reached by every
-//    thread on every path) and `griddepcontrol.wait`.
+//    order, so results are bit-reproducible.  The cluster exchange is `st.async` into the owner's shared memory,
+//    counted on the owner's mbarrier: a CTA goes on when its own slots are full, not when the whole cluster is done.
+//  * the waits are `bar.sync`, one cluster barrier at the start (both reached by every thread on every path),
+//    `griddepcontrol.wait`, and the wait on that mbarrier, which is bounded in time and reports through a status word.
 #include <algorithm>
 
 #include "w4a16_common.cuh"
+#include "w4a16_async.cuh"
 
 namespace kiln {
 namespace {
@@ -61,7 +63,7 @@ struct DecodeParams {
     int count;
     int warps_n, warps_k;
     int red_pitch;          // floats per reduction row (warps_n*64 + 4 or 8)
-    int off_red, off_recv, off_lora;  // shared-memory carve-up (bytes from the 128-byte aligned base)
+    int off_red, off_recv, off_lora, off_mbar;  // shared-memory carve-up (bytes from the 128-byte aligned base)
     int ppr_shift;          // log2 of the output pairs (two adjacent columns) per row of a CTA = 5 + log2(warps_n)
     int own_cols;           // receive slots per row owned by one rank of the cluster
     uint32_t own_magic;     // ceil(2^32 / own_cols): x / own_cols = umulhi(x, own_magic) for the small x used here
@@ -226,6 +228,30 @@ __device__ __forceinline__ void compute_unit_s(uint4 (&w)[8], const uint4 *next,
 }
 
 
+// Set (never cleared by a kernel) when a CTA gave up waiting for the split-K partial sums of its cluster peers;
+// kiln_w4a16_check_device_status reads and clears it.  A static word, so that no launch path allocates for it.
+__device__ uint32_t g_decode_status;
+
+// Store a float2 into a peer's shared memory; its 8 bytes count on the peer's mbarrier when they have landed.
+__device__ __forceinline__ void st_async_f2(uint32_t cluster_addr, float2 v, uint32_t cluster_mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1,%2}, [%3];" ::"r"(cluster_addr),
+                 "f"(v.x), "f"(v.y), "r"(cluster_mbar)
+                 : "memory");
+}
+
+// Wait for phase 0 of this CTA's exchange mbarrier.  Bounded in wall-clock time: a peer that never delivers makes
+// the CTA record 0x800 in the status word and leave without writing C.
+__device__ __forceinline__ bool mbar_wait_decode(uint32_t bar) {
+    if (mbar_try_wait(bar, 0)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, 0)) return true;
+        if ((i & 15) == 15 && global_ns() - t0 > kWaitLimitNs) break;
+    }
+    atomicCAS(&g_decode_status, 0u, 0x800u);
+    return false;
+}
+
 constexpr uint4 kOnesF16 = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 
 // grid = (cluster_k, sum over problems of n / (64*warps_n), ceil(max m / (8*NB))), cluster = (cluster_k, 1, 1),
@@ -257,14 +283,26 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
         for (int i = 0; i < 4; ++i) acc.t[j][i] = 0.f;
     {  // ---- streaming part: its coordinates and pointers go out of scope before the reduction ----
     const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
-    // A CTA may only be written through distributed shared memory once it is running: every CTA of the cluster
-    // announces itself here and checks the others just before the first remote store, long after.
-    if (csize > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthreads = blockDim.x;
     const int m0 = blockIdx.z * kRows;
     const int m_valid = min(kRows, q.m - m0);
+    // A CTA may only be written through distributed shared memory once it is running: every CTA of the cluster
+    // announces itself here and checks the others just before the first remote store, long after.  Before it does,
+    // it arms the mbarrier that counts the bytes of the split-K exchange it will receive: one float2 per valid row
+    // and owned column pair from every rank of the cluster, itself included.
+    if (csize > 1) {
+        if (tid == 0) {
+            const int ppr = 1 << p.ppr_shift;
+            const int mine = q.swiglu ? 2 * min(p.own_items, (ppr >> 1) - static_cast<int>(rank) * p.own_items)
+                                      : min(p.own_cols, ppr - static_cast<int>(rank) * p.own_cols);
+            mbar_init(base + p.off_mbar, 1);
+            mbar_init_fence();
+            mbar_arrive_expect_tx(base + p.off_mbar, csize * m_valid * max(mine, 0) * 8);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    }
+
     const int wn = warp % p.warps_n, wk = warp / p.warps_n;
     const int chunk = (static_cast<int>(blockIdx.y) - q.y0) * p.warps_n + wn;
     const int gc0 = min(q.groups, static_cast<int>(rank) * q.groups_per_cta);
@@ -433,9 +471,9 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
     // An output pair is two adjacent columns of one row.  The pairs of a row are dealt to the cluster ranks in
     // contiguous slices (SwiGLU: slices of items, an item being a gate pair and the up pair 32 columns after it, so
     // that both meet in one rank).  Every CTA sums its K-teams and pushes each pair into the owning rank's receive
-    // buffer, slot [sender rank][row][slot of the pair]; after ONE cluster barrier the owner adds the slots in rank
-    // order, finishes the values (per-column scale, LoRA delta, SwiGLU) and writes C.  Nobody touches a peer's
-    // shared memory after that barrier, so CTAs may exit without a second one.  Everything here is a chain of
+    // buffer, slot [sender rank][row][slot of the pair], with stores that count their bytes on the owner's mbarrier;
+    // once its slots are full the owner adds them in rank order, finishes the values (per-column scale, LoRA delta,
+    // SwiGLU) and writes C.  Everything here is a chain of
     // dependent instructions in few threads, so it avoids divisions and keeps the shared-memory loads of a sum
     // independent of each other.
     const int ppr_shift = p.ppr_shift, ppr = 1 << ppr_shift;
@@ -521,9 +559,13 @@ __global__ void __launch_bounds__(NB == 1 ? KILN_DECODE_LB1 : 512, 1) w4a16_deco
             owner = __umulhi(it, p.item_magic);
             j = 2 * (it - owner * p.own_items) + ((cp >> 4) & 1);
         }
-        st_dsmem_f2(map_to_cta(recv_base + 8u * ((rank * kRows + row) * p.own_cols + j), owner), v);
+        st_async_f2(map_to_cta(recv_base + 8u * ((rank * kRows + row) * p.own_cols + j), owner), v,
+                    map_to_cta(base + p.off_mbar, owner));
     }
-    cluster_sync_all();
+    // Each CTA goes on as soon as ITS slots are complete (no barrier over the cluster): the stores above count
+    // their bytes on the owner's mbarrier.  A CTA that has received everything has nothing left that a peer writes,
+    // and its own stores need nothing of it once issued, so it may exit without a second cluster barrier.
+    if (!mbar_wait_decode(base + p.off_mbar)) return;
     {
         const float2 *recv = reinterpret_cast<const float2 *>(base_gen + p.off_recv);
         const int slot_stride = kRows * p.own_cols;
@@ -623,12 +665,15 @@ DecodeConfig choose_config(int m, int n, int k, const DecodeOverride &ov) {
             int k, n, m_max, ck, wk, wn;
         };
         static const Tuned kTuned[] = {
-            {2560, 4096, 2, 5, 4, 2},    {2560, 4096, 8, 4, 5, 4},   {2560, 4096, 16, 4, 5, 2},   // q
-            {2560, 512, 8, 8, 3, 1},     {2560, 512, 16, 5, 4, 1},                                // k, v
-            {4096, 2560, 2, 4, 8, 1},    {4096, 2560, 8, 8, 4, 2},   {4096, 2560, 16, 6, 6, 2},   // o, GDN-out
-            {2560, 18432, 2, 1, 10, 1},  {2560, 18432, 8, 2, 5, 2},  {2560, 18432, 16, 2, 4, 4},  // gate+up
+            {2560, 4096, 4, 5, 4, 2},    {2560, 4096, 8, 4, 5, 4},   {2560, 4096, 16, 4, 5, 2},   // q
+            {2560, 512, 2, 8, 3, 1},     {2560, 512, 4, 5, 4, 2},    {2560, 512, 8, 8, 3, 4},     // k, v
+            {2560, 512, 16, 5, 4, 1},
+            {4096, 2560, 2, 4, 8, 1},    {4096, 2560, 4, 8, 4, 2},   {4096, 2560, 8, 8, 4, 4},    // o, GDN-out
+            {4096, 2560, 16, 6, 6, 2},
+            {2560, 18432, 1, 1, 10, 1},  {2560, 18432, 8, 2, 5, 2},  {2560, 18432, 16, 2, 4, 4},  // gate+up
             {9216, 2560, 2, 6, 8, 1},    {9216, 2560, 16, 6, 6, 2},                               // down
-            {2560, 8192, 2, 1, 12, 1},   {2560, 8192, 8, 1, 20, 1},  {2560, 8192, 16, 4, 4, 4},   // GDN-in
+            {2560, 8192, 1, 1, 12, 1},   {2560, 8192, 2, 5, 4, 1},   {2560, 8192, 4, 4, 5, 2},    // GDN-in
+            {2560, 8192, 8, 4, 5, 4},    {2560, 8192, 16, 4, 4, 4},
         };
         for (const Tuned &t : kTuned)
             if (t.k == k && t.n == n && m <= t.m_max && t.wk * t.wn <= kMaxWarps[c.nb]) {
@@ -692,7 +737,8 @@ int launch_list(DecodeParams &p, int ck, int max_m, cudaStream_t stream) {
     p.own_magic = static_cast<uint32_t>(((1ull << 32) + p.own_cols - 1) / p.own_cols);
     p.item_magic = static_cast<uint32_t>(((1ull << 32) + p.own_items - 1) / p.own_items);
     p.off_lora = p.off_recv + align(ck > 1 ? 8 * (ck * 8 * NB * p.own_cols) : 0, 128);
-    const size_t smem = static_cast<size_t>(p.off_lora) + lora_bytes + 128;
+    p.off_mbar = p.off_lora + align(lora_bytes, 16);
+    const size_t smem = static_cast<size_t>(p.off_mbar) + 16 + 128;
     if (smem > kMaxSmem) return KILN_W4A16_ERR_KERN_SHAPE;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ck, grid_y, (max_m + 8 * NB - 1) / (8 * NB));
@@ -785,6 +831,20 @@ int launch_decode(const GemmArgs &a, const DecodeOverride &ov) {
     it.lora_r = a.lora_r;
     it.swiglu = a.swiglu;
     return launch_decode_list(&it, 1, a.stream, ov);
+}
+
+// Reads and clears this device's decode status word (set when a CTA gave up waiting for its cluster peers).
+int decode_status_read_clear(cudaStream_t st, uint32_t *out) {
+    *out = 0;
+    void *w = nullptr;
+    if (int rc = record_cuda_error(cudaGetSymbolAddress(&w, g_decode_status))) return rc;
+    if (int rc = record_cuda_error(cudaMemcpyAsync(out, w, sizeof(uint32_t), cudaMemcpyDeviceToHost, st))) return rc;
+    if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
+    if (*out != 0) {
+        if (int rc = record_cuda_error(cudaMemsetAsync(w, 0, sizeof(uint32_t), st))) return rc;
+        if (int rc = record_cuda_error(cudaStreamSynchronize(st))) return rc;
+    }
+    return 0;
 }
 
 }  // namespace kiln

@@ -168,5 +168,6 @@ void prefill_plan(int m, int n, int k, int out[4]);
 bool prefill_supported(int m, int n, int k, int groupsize);
 bool prefill_fuses_swiglu(int m, int n, int k);
 int static_status_read_clear(cudaStream_t st, uint32_t *out);
+int decode_status_read_clear(cudaStream_t st, uint32_t *out);
 
 }  // namespace kiln

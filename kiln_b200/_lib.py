@@ -69,6 +69,7 @@ SIGNATURES = {
     "kiln_w4a16_set_decode_override": (None, [_i, _i, _i]),
     "kiln_w4a16_decode_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "kiln_w4a16_set_prefill_override": (None, [_i, _i, _i, _i]),
+    "kiln_w4a16_set_small_batch_kernel": (None, [_i]),
     "kiln_w4a16_set_wait_limit_ns": (None, [ctypes.c_ulonglong]),
     "kiln_w4a16_test_drop_activation_load": (None, [_i]),
     "kiln_w4a16_prefill_plan": (None, [_i, _i, _i, ctypes.POINTER(ctypes.c_int)]),

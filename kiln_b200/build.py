@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkiln_w4a16.so")
-SOURCES = ["api.cu", "decode_w4a16.cu", "epilogue_w4a16.cu", "prefill_w4a16_umma.cu", "repack.cu"]
+SOURCES = ["api.cu", "decode_w4a16.cu", "epilogue_w4a16.cu", "prefill_w4a16_umma.cu", "repack.cu", "smallm_w4a16_tmem.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",

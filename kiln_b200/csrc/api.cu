@@ -83,20 +83,28 @@ static int validate(const GemmArgs &a) {
 //    provided the activation matrix is at least 128 KB (smaller ones were measured 40 % slower through its TMA loads);
 //  * projections of 1024 columns or fewer (k, v: four to eight tiles) stay on the decode kernel up to M = 256
 //    (k at M=128: 6.4 / 15.3).
+//  * a GEMM without epilogue options, grouped scales and at most 64 rows runs on the tcgen05 kernel that keeps the
+//    weights in tensor memory (smallm_w4a16_tmem.cu), which moves the crossover to 17 rows for every projection of more
+//    than 1024 columns (M=17: q 7.8 / 6.8, gate+up 18.3 / 13.6, down 12.8 / 10.1, GDN-in 11.0 / 10.0, o 9.1 / 7.0;
+//    M=16, one block of the decode kernel: q 5.7 / 6.6, gate+up 12.0 / 13.4).
 // kiln_w4a16_set_prefill_min_m replaces the rule by a plain threshold.
-static bool use_prefill(int m, int n, int k, int groupsize) {
+static bool use_prefill(int m, int n, int k, int groupsize, bool plain = false) {
     if (!prefill_supported(m, n, k, groupsize)) return false;
     const int min_m = g_prefill_min_m.load(std::memory_order_relaxed);
     if (min_m != kDefaultPrefillMinM) return m >= min_m;
     if (n <= 1024) return m > 256;
+    if (plain && m <= 64 && smallm_supported(m, n, k, groupsize)) return m >= 17;
     if (n <= 3072 && static_cast<long long>(m) * k * 2 >= (128LL << 10)) return m >= 17;
     return m >= 33;
 }
 
+// no epilogue option and no fused all-gather: what the small-batch tcgen05 kernel takes
+static bool plain_gemm(const GemmArgs &a) { return !a.swiglu && a.lora_r == 0 && a.n_peers == 0 && !a.mc_c && !a.no_scratch; }
+
 static int gemm(const GemmArgs &a) {
     const int v = validate(a);
     if (v >= 0) return v;
-    if (use_prefill(a.m, a.n, a.k, a.groupsize)) {
+    if (use_prefill(a.m, a.n, a.k, a.groupsize, plain_gemm(a))) {
         const size_t need = a.no_scratch ? 0 : prefill_workspace_bytes(a.m, a.n, a.k);
         if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
         return launch_prefill(a);
@@ -264,7 +272,7 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_grouped(const kiln_w4a16_problem_t *pro
         const int v = validate(a);
         if (v > 0) return v;
         if (v == 0) continue;  // an empty problem
-        if (use_prefill(q.m, q.n, q.k, q.groupsize)) one_launch = false;
+        if (use_prefill(q.m, q.n, q.k, q.groupsize)) one_launch = false;  // (one decode launch for the group beats per-problem small-batch launches)
         items[live++] = DecodeItem{q.A, q.B, q.s, q.C, q.m, q.n, q.k, q.groupsize, nullptr, nullptr, 0, 0};
     }
     if (live == 0) return KILN_W4A16_OK;
@@ -282,7 +290,7 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_grouped(const kiln_w4a16_problem_t *pro
 
 size_t kiln_w4a16_workspace_bytes(int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
-    if (use_prefill(m, n, k, 128)) return prefill_workspace_bytes(m, n, k);
+    if (use_prefill(m, n, k, 128, true)) return prefill_workspace_bytes(m, n, k);
     return 0;
 }
 
@@ -316,6 +324,8 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n) {
 void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]) {
     if (out && m > 0 && n > 0 && k > 0) decode_plan(m, n, k, g_decode_override, out);
 }
+
+void kiln_w4a16_set_small_batch_kernel(int enabled) { set_smallm_enabled(enabled); }
 
 void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k) {
     set_prefill_override(bn, splits, m_tiles, stream_k);

@@ -121,11 +121,17 @@ struct WorkIter {
 // the epilogue adds the two accumulators.
 // KS = 64-deep K atoms per pipeline stage: with KS = 2 a stage holds 128 K-elements (one scale group), which halves the
 // barrier round trips, waits and commits per K of the small tiles that are bound by them.
-template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1>
+// AR = activation rows that a stage holds per 64-deep atom: 128 (a whole M-tile), or 64 when the problem has at most 64
+// rows.  The MMA still reads 128 rows; rows 64..127 then alias whatever follows the atom in the stage (the next atom or
+// the weight tile: finite or not, they only reach accumulator rows that are never stored).  The 8 KB saved per atom buy
+// a deeper pipeline (4 stages of 48 KB instead of 3 of 64 KB), and these problems are bound by the round trip
+// stage free -> TMA load / dequant -> MMA -> commit, not by any throughput.
+template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1, int AR = BM>
 struct Cfg {
     static_assert(KP == 1 || (KP == 2 && MT == 1 && BN == 128), "K-parity issuers: one M-tile of 128 columns only");
     static_assert(KS == 1 || KS == 2, "one or two 64-deep atoms per stage");
-    static constexpr int kAAtomBytes = MT * BM * BK * 2;  // one 64-deep atom of the activation tile(s)
+    static_assert(AR == BM || (AR == 64 && MT == 1), "half-height activation atoms: one M-tile only");
+    static constexpr int kAAtomBytes = MT * AR * BK * 2;  // one 64-deep atom of the activation tile(s)
     static constexpr int kBAtomBytes = BN * BK * 2;
     static constexpr int kIssuers = MT == 2 ? 2 : KP;
     static constexpr int kGroupWarps = DW / DG;
@@ -154,11 +160,11 @@ struct DequantRegs {
     uint4 w[NBLK];
 };
 
-template <int BN, int MT, int DW, int DG, int KP, int KS>
+template <int BN, int MT, int DW, int DG, int KP, int KS, int AR>
 __global__ void __launch_bounds__((6 + DW + ((MT == 2 || KP == 2) ? 1 : 0)) * 32, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
                      const __grid_constant__ CUtensorMap tmap_t, const __grid_constant__ CUtensorMap tmap_lb, const PrefillParams p) {
-    using C = Cfg<BN, MT, DW, DG, KP, KS>;
+    using C = Cfg<BN, MT, DW, DG, KP, KS, AR>;
     using Regs = DequantRegs<C::kBlocksPerWarp>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -824,6 +830,7 @@ StreamKPlan streamk_plan(int tiles, int k_iters, int grid) {
 PrefillConfig g_prefill_override{0, 0, 0, 0};
 unsigned long long g_wait_limit_ns = kWaitLimitNs;
 int g_test_drop_a_load = -1;
+int g_smallm_enabled = 1;
 
 PrefillConfig choose_prefill(int m, int n, int k, bool allow_pairs = true, bool allow_scratch = true,
                              size_t max_split_bytes = ~static_cast<size_t>(0)) {
@@ -891,16 +898,16 @@ bool encode_c_map(EncodeTiledFn enc, CUtensorMap *map, void *c, int m, int n) {
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1>
+template <int BN, int MT = 1, int DW = 8, int DG = 2, int KP = 1, int KS = 1, int AR = BM>
 int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams p, cudaStream_t stream,
               const CUtensorMap *tmap_t = nullptr, const CUtensorMap *tmap_lb = nullptr) {
-    using C = Cfg<BN, MT, DW, DG, KP, KS>;
+    using C = Cfg<BN, MT, DW, DG, KP, KS, AR>;
     p.k_iters /= KS;  // the kernel counts pipeline stages of KS atoms (k is a multiple of 128)
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS>,
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS, AR>,
                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)))
             return rc;
         attr_set[dev] = true;
@@ -918,7 +925,7 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams 
     cfg.numAttrs = 1;
     static const CUtensorMap kNoMap = {};  // (never dereferenced when p.lora_steps == 0)
     if (!tmap_t || !tmap_lb || KS != 1) p.lora_steps = 0;
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS>, tmap, tmap_c,
+    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_prefill_kernel<BN, MT, DW, DG, KP, KS, AR>, tmap, tmap_c,
                                                 tmap_t ? *tmap_t : kNoMap, tmap_lb ? *tmap_lb : kNoMap, p));
 }
 
@@ -937,6 +944,8 @@ bool prefill_fuses_swiglu(int m, int n, int k) {
 bool prefill_fuses_lora(int groupsize, int lora_r) { return groupsize == 128 && lora_r > 0 && lora_r <= 128 && lora_r % 8 == 0; }
 
 void set_wait_limit_ns(unsigned long long ns) { g_wait_limit_ns = ns ? ns : kWaitLimitNs; }
+unsigned long long current_wait_limit_ns() { return g_wait_limit_ns; }
+void set_smallm_enabled(int on) { g_smallm_enabled = on; }
 void set_test_drop_a_load(int k_step) { g_test_drop_a_load = k_step; }
 
 void set_prefill_override(int bn, int splits, int mt, int stream_k) {
@@ -972,11 +981,31 @@ int launch_prefill(const GemmArgs &a) {
     const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused && !a.no_scratch);
     if (a.swiglu && (fused || c.splits != 1 || c.stream_k || (c.bn == 128 && c.mt == 1)))
         return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_swiglu first)
+    // At most 64 rows in 128-column tiles: the kernel that keeps the dequantised weights in tensor memory (same tiling,
+    // same K splits and workspace, so everything the planner reports holds for it too)
+    if (g_smallm_enabled && !fused && !a.swiglu && a.lora_r == 0 && g_test_drop_a_load < 0 && c.bn == 128 && c.mt == 1 &&
+        !c.stream_k && c.splits <= a.k / 128 && smallm_supported(a.m, a.n, a.k, a.groupsize)) {
+        const size_t need = workspace_for(c, a.m, a.n);
+        if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
+        int rc = launch_smallm(a, c.splits, static_cast<float *>(a.workspace));
+        if (rc == 0 && c.splits > 1) {
+            const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;
+            int blocks = static_cast<int>((total4 + 255) / 256);
+            const int cap = device_sm_count() * 8;
+            if (blocks > cap) blocks = cap;
+            note_launch();
+            rc = record_cuda_error(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), a.stream, static_cast<float *>(a.workspace),
+                                              static_cast<__nv_bfloat16 *>(a.C), static_cast<const __half *>(a.S), a.m, a.n, c.splits, 0));
+        }
+        return rc;
+    }
 
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.k) * 2};
-    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(BM * c.mt)};
+    // at most 64 rows in 128-column tiles of one M-tile: half-height activation atoms (AR = 64)
+    const bool half_a = a.m <= 64 && c.mt == 1 && c.bn == 128;
+    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(half_a ? 64 : BM * c.mt)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.A), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1032,7 +1061,7 @@ int launch_prefill(const GemmArgs &a) {
         const cuuint64_t td[2] = {static_cast<cuuint64_t>(a.lora_r), static_cast<cuuint64_t>(a.m)};
         const cuuint64_t ld[2] = {static_cast<cuuint64_t>(a.lora_r), static_cast<cuuint64_t>(a.n)};
         const cuuint64_t st[1] = {static_cast<cuuint64_t>(a.lora_r) * 2};
-        const cuuint32_t tb[2] = {BK, static_cast<cuuint32_t>(BM * c.mt)}, lb[2] = {BK, static_cast<cuuint32_t>(c.bn)};
+        const cuuint32_t tb[2] = {BK, static_cast<cuuint32_t>(half_a ? 64 : BM * c.mt)}, lb[2] = {BK, static_cast<cuuint32_t>(c.bn)};
         if (enc(&tmap_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.lora_t), td, st, tb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
             enc(&tmap_lb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.lora_b), ld, st, lb, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1063,9 +1092,11 @@ int launch_prefill(const GemmArgs &a) {
         if (c.bn == 256)
             rc = launch_bn<256, 1>(tmap, tmap_c, p, a.stream, pt, plb);
         else if (c.stream_k || a.k / 128 < c.splits || lora)  // (the LoRA steps are 64 deep)
-            rc = launch_bn<128, 1, 8, 2, 2, 1>(tmap, tmap_c, p, a.stream, pt, plb);
+            rc = half_a ? launch_bn<128, 1, 8, 2, 2, 1, 64>(tmap, tmap_c, p, a.stream, pt, plb)
+                        : launch_bn<128, 1, 8, 2, 2, 1>(tmap, tmap_c, p, a.stream, pt, plb);
         else
-            rc = launch_bn<128, 1, 8, 2, 2, 2>(tmap, tmap_c, p, a.stream);
+            rc = half_a ? launch_bn<128, 1, 8, 2, 2, 2, 64>(tmap, tmap_c, p, a.stream)
+                        : launch_bn<128, 1, 8, 2, 2, 2>(tmap, tmap_c, p, a.stream);
     if (rc) return rc;
     if (c.splits > 1) {
         const size_t total4 = static_cast<size_t>(a.m) * a.n / 4;

@@ -163,6 +163,10 @@ int launch_prefill(const GemmArgs &a);
 size_t prefill_workspace_bytes(int m, int n, int k);
 void set_prefill_override(int bn, int splits, int mt, int stream_k);
 void set_wait_limit_ns(unsigned long long ns);
+unsigned long long current_wait_limit_ns();
+void set_smallm_enabled(int on);
+bool smallm_supported(int m, int n, int k, int groupsize);
+int launch_smallm(const GemmArgs &a, int splits, float *partial);
 void set_test_drop_a_load(int k_step);
 void prefill_plan(int m, int n, int k, int out[4]);
 bool prefill_supported(int m, int n, int k, int groupsize);

@@ -237,11 +237,17 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
         const int quarter = warp & 3, ch = quarter >> 1, hf = quarter & 1;
         const int c = lane >> 2, qd = lane & 3;
         const int chunks_n = p.n >> 6;
-        // byte-permute selectors of the quad exchange (see the loop)
-        const uint32_t selS = (qd & 1) ? 0x5410u : 0x7632u, selK = (qd & 1) ? 0x7632u : 0x5410u;
-        const uint32_t selU = (qd & 1) ? 0x1054u : 0x5410u, selV = (qd & 1) ? 0x3276u : 0x7632u;
+        // Byte-permute selectors of the quad exchange (see the loop).  Bytes of a packed word: 0 = column 16j+c, even K;
+        // 1 = column 16j+8+c, even K; 2, 3 = the same columns, odd K; in each byte the low nibble is K pair qd, the high
+        // nibble K pair qd+4.  "Item" i = {even byte, odd byte} of the lane's column i = 2*(j - 2hf) + e: bytes (0,2) and
+        // (1,3) of the lane's first word, (4,6) and (5,7) of its second.
+        const uint32_t selK = (qd & 1) ? 0x7531u : 0x6420u;  // the two items this lane keeps in the exchange with lane qd^1 ...
+        const uint32_t selS = (qd & 1) ? 0x6420u : 0x7531u;  // ... and the two it sends
+        // after it, {kept, received} hold items {b0, 2+b0} (b0 = qd%2) of the lane pair's two source lanes; ordered by source:
+        const uint32_t selU = (qd & 1) ? 0x1054u : 0x5410u, selV = (qd & 1) ? 0x3276u : 0x7632u;  // item b0 / item 2+b0
+        const uint32_t selK2 = (qd & 2) ? selV : selU;       // exchange with lane qd^2: keep the item this lane owns (item qd) ...
+        const uint32_t selS2 = (qd & 2) ? selU : selV;       // ... send the other
         const uint32_t selRa = (qd & 2) ? 0x7564u : 0x3120u, selRb = (qd & 2) ? 0x3120u : 0x7564u;
-        const bool hi2 = (qd & 2) != 0;
         // this lane's column after the exchange is 16 * (2hf + qd/2) + 8 * (qd%2) + c of chunk ch; its scale sits at
         // 8c + 2hf*2 + qd of the chunk's scale order (position 8i + t holds column 8t + i)
         const int scale_off = ch * 64 + 8 * c + 4 * hf + qd;
@@ -285,16 +291,12 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
                     tc_fence_after();
 #pragma unroll
                     for (int kt = 0; kt < 8; ++kt) {
-                        // Bytes of a packed word: 0 = column 16j+c, even K; 1 = column 16j+8+c, even K; 2, 3 = the same
-                        // columns, odd K; in each byte the low nibble is K pair qd, the high nibble K pair qd+4.
-                        // item i = {even byte, odd byte} of the lane's column i (i = 2*(j - 2hf) + e): four 16-bit items.
-                        const uint32_t p01 = prmt(rw[v][kt].x, 0u, 0x3120u), p23 = prmt(rw[v][kt].y, 0u, 0x3120u);
-                        // 4 x 4 transpose of the items over the quad: lane qd ends up with item qd of lanes 0..3
-                        const uint32_t keep1 = prmt(p01, p23, selK);
-                        const uint32_t recv1 = __shfl_xor_sync(0xFFFFFFFFu, prmt(p01, p23, selS), 1);
-                        const uint32_t uu = prmt(keep1, recv1, selU), vv = prmt(keep1, recv1, selV);
-                        const uint32_t keep2 = hi2 ? vv : uu;
-                        const uint32_t recv2 = __shfl_xor_sync(0xFFFFFFFFu, hi2 ? uu : vv, 2);
+                        // 4 x 4 transpose of the 16-bit items over the quad, on the packed bytes: lane qd ends up with item qd
+                        // (its column) of lanes 0..3, i.e. all eight K pairs of the 16-row K tile
+                        const uint32_t keep1 = prmt(rw[v][kt].x, rw[v][kt].y, selK);
+                        const uint32_t recv1 = __shfl_xor_sync(0xFFFFFFFFu, prmt(rw[v][kt].x, rw[v][kt].y, selS), 1);
+                        const uint32_t keep2 = prmt(keep1, recv1, selK2);
+                        const uint32_t recv2 = __shfl_xor_sync(0xFFFFFFFFu, prmt(keep1, recv1, selS2), 2);
                         // ra: even-K nibbles of K pairs 0, 4, 1, 5 in bits 0..15, the odd-K ones in bits 16..31; rb: pairs 2, 6, 3, 7
                         const uint32_t ra = prmt(keep2, recv2, selRa), rb = prmt(keep2, recv2, selRb);
                         uint32_t r[8];

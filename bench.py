@@ -259,6 +259,31 @@ def decode_detail(d: Device, peaks):
     return out
 
 
+def small_batch_detail(d: Device, peaks):
+    """Continuous-batching row counts (24, 64 and 128 rows) on the four large projections: the tcgen05 kernel that keeps the
+    dequantised weights in tensor memory.  Microseconds per launch in a CUDA graph over rotating weight copies, algorithmic
+    GB/s and fraction of the measured HBM peak (these sizes are still bound by the weight stream's dequantisation)."""
+    out = {}
+    for name in ("q", "gate_up", "down", "gdn_in"):
+        k, n = SHAPES[name]
+        copies = max(2, min(64, int(2.2 * L2_BYTES / (k * n / 2)) + 1))
+        ws = d.weights(k, n, copies)
+        for m in (24, 64, 128):
+            a = d.acts(m, k)
+            o = d.torch.empty((m, n), dtype=d.torch.bfloat16, device=d.dev)
+            nl = max(copies, 24)
+
+            def fn():
+                for i in range(nl):
+                    d.gemm(a, ws[i % copies], o)
+
+            us = d.time_graph(fn, nl, reps=5)
+            gbs = alg_bytes(m, k, n) / us / 1e3
+            out[f"{name}:m{m}"] = {"us": round(us, 2), "GBps": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4)}
+        del ws
+    return out
+
+
 def fused_rows_detail(d: Device, peaks):
     """Sibling projections as the library recommends issuing them: q, k, v of an attention layer in ONE grouped launch,
     and gate+up with SwiGLU fused into the epilogue (interleaved columns, [m, 9216] output).  Algorithmic bytes are
@@ -890,6 +915,8 @@ def run_ours(args):
         if world == 1:
             line["config0"] = config0_detail(d, peaks)
         line["prefill"] = prefill_detail(d, peaks)
+        if world == 1:
+            line["small_batch"] = small_batch_detail(d, peaks)
         line["stack_m64"] = stack_detail(d, 64)
         if world == 1:
             line["pack"] = pack_detail(d)

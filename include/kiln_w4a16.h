@@ -246,7 +246,7 @@ void kiln_w4a16_set_prefill_min_m(int min_m);
  * the reference. */
 void kiln_w4a16_set_prefill_override(int bn, int splits, int m_tiles, int stream_k);
 
-/* Tuning hook: 0 keeps problems of at most 64 rows on the general tcgen05 kernel instead of the one that holds the
+/* Tuning hook: 0 keeps problems of at most 128 rows on the general tcgen05 kernel instead of the one that holds the
  * dequantised weights in tensor memory (default 1).  Results of the two kernels are the same up to fp32 summation
  * order.  Process-wide, not thread-safe; no counterpart in the reference. */
 void kiln_w4a16_set_small_batch_kernel(int enabled);

@@ -981,7 +981,7 @@ int launch_prefill(const GemmArgs &a) {
     const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused && !a.no_scratch);
     if (a.swiglu && (fused || c.splits != 1 || c.stream_k || (c.bn == 128 && c.mt == 1)))
         return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_swiglu first)
-    // At most 64 rows in 128-column tiles: the kernel that keeps the dequantised weights in tensor memory (same tiling,
+    // At most 128 rows in 128-column tiles: the kernel that keeps the dequantised weights in tensor memory (same tiling,
     // same K splits and workspace, so everything the planner reports holds for it too)
     if (g_smallm_enabled && !fused && !a.swiglu && a.lora_r == 0 && g_test_drop_a_load < 0 && c.bn == 128 && c.mt == 1 &&
         !c.stream_k && c.splits <= a.k / 128 && smallm_supported(a.m, a.n, a.k, a.groupsize)) {

@@ -1,4 +1,4 @@
-// W4A16 GEMM for 17..64 activation rows on sm_100a: the dequantised weights are the TENSOR-MEMORY operand of tcgen05.mma.
+// W4A16 GEMM for 17..128 activation rows on sm_100a: the dequantised weights are the TENSOR-MEMORY operand of tcgen05.mma.
 //
 // The general tcgen05 kernel (prefill_w4a16_umma.cu) dequantises a 128-column weight tile into shared memory, where the
 // MMA reads it back together with a 128-row activation tile.  For a problem with few rows that is bound by shared-memory
@@ -9,8 +9,8 @@
 //  * the 128 weight columns of a tile are the M = 128 rows of the MMA, one per TMEM lane, and the dequant warps write
 //    them straight into tensor memory with tcgen05.st (bf16 pairs of consecutive K per 32-bit cell); they never
 //    touch shared memory;
-//  * the activations are the N operand (N = rows rounded up to 16, at most 64), K-major 128B-swizzled tiles that TMA
-//    drops into shared memory: 16 KB per 128 K written once and read once;
+//  * the activations are the N operand (N = rows rounded up to 16, at most 128), K-major 128B-swizzled tiles that TMA
+//    drops into shared memory: at most 32 KB per 128 K, written once and read once;
 //  * the accumulator is 128 lanes x N fp32 columns; a thread of the epilogue owns one output column.
 // A packed word of the kiln-marlin-gemm layout (kiln-marlin-gemm/src/lib.rs:262-357) gives a lane two K pairs of eight
 // columns, but a TMEM lane needs all K of ONE column: the four lanes of a quad exchange their PACKED bytes (two
@@ -28,11 +28,12 @@ namespace kiln {
 namespace {
 
 constexpr int kTileCols = 128;                   // weight columns per tile = TMEM lanes = MMA M
-constexpr int kMaxRows = 64;                     // activation rows = MMA N (rounded up to 16)
+constexpr int kMaxRows = 128;                    // most activation rows = MMA N (rounded up to 16) the kernel takes
 constexpr int kStageK = 128;                     // K per pipeline stage: one scale group, eight K=16 MMAs
 constexpr int kStages = 4;
-constexpr int kXAtomBytes = kMaxRows * 128;      // 64 rows x 64 bf16, 128B-swizzled
-constexpr int kXStageBytes = 2 * kXAtomBytes;    // 16 KB
+// The kernel comes in two sizes, R = 64 or 128 rows: an activation atom is R rows x 64 bf16 (128B-swizzled), a stage
+// two atoms, an accumulator R fp32 columns.  R = 64 has two accumulator buffers per issuer (a CTA with several units
+// drains one while the next fills), R = 128 one: 4 x 64 + 2 x 2 x 64 = 4 x 64 + 2 x 128 = 512 TMEM columns either way.
 constexpr int kWStageCols = kStageK / 2;         // TMEM columns of one stage of weights (two bf16 per cell)
 constexpr int kAccBase = kStages * kWStageCols;  // accumulators start at TMEM column 256
 constexpr int kTmemCols = 512;                   // 256 weights + 2 buffers x 2 issuers x 64 accumulator columns
@@ -40,7 +41,8 @@ constexpr int kDequantWarp0 = 6, kTeamWarps = 4, kTeams = 2;
 constexpr int kIssuerWarp2 = kDequantWarp0 + kTeamWarps * kTeams;
 constexpr int kThreads = (kIssuerWarp2 + 1) * 32;
 constexpr int kBarrierBytes = 256;
-constexpr int kSmemBytes = kStages * kXStageBytes + kBarrierBytes + 1024;  // + alignment slack
+template <int R>
+constexpr int smem_bytes() { return kStages * 2 * R * 128 + kBarrierBytes + 1024; }  // + alignment slack
 
 struct SmallMParams {
     const uint2 *B;  // packed weights seen as 8-byte halves of the 16-byte lane pieces
@@ -91,8 +93,11 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t d_tmem, uint32_t a_tme
         : "memory");
 }
 
+template <int R>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMParams p) {
+    constexpr int kXAtomBytes = R * 128, kXStageBytes = 2 * kXAtomBytes;
+    constexpr int kAccBufs = R == 64 ? 2 : 1;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -176,8 +181,8 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
                 unit_range(u, nt, sp, ks0, ks1);
-                const uint32_t acc = tile & 1, acc_ph = (tile >> 1) & 1;
-                const uint32_t d_tmem = tmem_base + kAccBase + (acc * 2 + q) * kMaxRows;
+                const uint32_t acc = tile % kAccBufs, acc_ph = (tile / kAccBufs) & 1;
+                const uint32_t d_tmem = tmem_base + kAccBase + (acc * 2 + q) * R;
                 for (int ks = ks0; ks < ks1; ++ks, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
@@ -206,15 +211,15 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
         bool ok = true;
         for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++tile) {
             unit_range(u, nt, sp, ks0, ks1);
-            const uint32_t acc = tile & 1, acc_ph = (tile >> 1) & 1;
+            const uint32_t acc = tile % kAccBufs, acc_ph = (tile / kAccBufs) & 1;
             if (!(ok = mbar_wait(tmem_full(acc), acc_ph, abort_flag, p.status, 0xD00u | acc, p.wait_limit_ns))) break;
             tc_fence_after();
-            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccBase + acc * 2 * kMaxRows;
+            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccBase + acc * 2 * R;
             const size_t col = static_cast<size_t>(nt) * kTileCols + col_in_tile;
             for (int r0 = 0; r0 < p.npad; r0 += 16) {
                 uint32_t a[16], b[16];
                 tmem_ld_32x32b_x16(t0 + r0, a);
-                tmem_ld_32x32b_x16(t0 + kMaxRows + r0, b);
+                tmem_ld_32x32b_x16(t0 + R + r0, b);
                 tmem_ld_wait();
                 if (p.splits == 1) {
 #pragma unroll
@@ -340,7 +345,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
 
 }  // namespace
 
-// Shapes this kernel takes: 17..64 rows would all work, the dispatcher decides from which row count it pays.
+// Shapes this kernel takes (any row count up to 128 works; the dispatcher decides from which one it pays).
 bool smallm_supported(int m, int n, int k, int groupsize) {
     return m >= 1 && m <= kMaxRows && groupsize == 128 && n % kTileCols == 0 && k % kStageK == 0;
 }
@@ -382,7 +387,9 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_smallm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)))
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_smallm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<64>())))
+            return rc;
+        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_smallm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<128>())))
             return rc;
         attr_set[dev] = true;
     }
@@ -390,13 +397,14 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(units < device_sm_count() ? units : device_sm_count());
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.dynamicSmemBytes = a.m <= 64 ? smem_bytes<64>() : smem_bytes<128>();
     cfg.stream = a.stream;
     cudaLaunchAttribute attr = pdl_attribute();
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     note_launch();
-    return record_cuda_error(cudaLaunchKernelEx(&cfg, w4a16_smallm_kernel, tmap, p));
+    return record_cuda_error(a.m <= 64 ? cudaLaunchKernelEx(&cfg, w4a16_smallm_kernel<64>, tmap, p)
+                                       : cudaLaunchKernelEx(&cfg, w4a16_smallm_kernel<128>, tmap, p));
 }
 
 }  // namespace kiln

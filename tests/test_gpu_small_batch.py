@@ -1,5 +1,5 @@
-"""GPU parity of the small-batch tcgen05 kernel (at most 64 rows; the dequantised weights live in tensor memory), through
-the C ABI.
+"""GPU parity of the small-batch tcgen05 kernel (at most 128 rows; the dequantised weights live in tensor memory),
+through the C ABI.
 
 Each case is checked against the fp64 oracle (every row), against a float32 torch matmul of the dequantised weight,
 and bit for bit against the general tcgen05 kernel on the same inputs: both dequantise with the same two bf16 roundings
@@ -44,10 +44,12 @@ def _run(case, small_batch, m, n, device):
     return out
 
 
-# one K stage, one tile; ragged row counts around the MMA's N steps of 16; K splits (q: 4, down: 6); many tiles per CTA
+# one K stage, one tile; ragged row counts around the MMA's N steps of 16; K splits (q: 4, down: 6); many tiles per CTA;
+# the 128-row variant (65..128 rows: one accumulator buffer)
 @pytest.mark.parametrize("m,k,n", [(1, 128, 256), (16, 256, 256), (17, 640, 512), (31, 2560, 4096), (33, 4096, 2560),
                                    (47, 9216, 2560), (48, 2560, 8192), (64, 2560, 18432), (64, 128, 256),
-                                   (63, 1152, 38400)])
+                                   (63, 1152, 38400), (65, 2560, 4096), (100, 9216, 2560),
+                                   (128, 2560, 18432), (127, 640, 512)])
 def test_small_batch_kernel_matches_the_oracle_and_the_general_kernel(cuda_device, m, k, n):
     case = _case(m, k, n, seed=3 * m + k + n, device=cuda_device)
     out = _run(case, True, m, n, cuda_device)

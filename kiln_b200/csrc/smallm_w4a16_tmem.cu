@@ -1,10 +1,10 @@
 // W4A16 GEMM for 17..128 activation rows on sm_100a: the dequantised weights are the TENSOR-MEMORY operand of tcgen05.mma.
 //
 // The general tcgen05 kernel (prefill_w4a16_umma.cu) dequantises a 128-column weight tile into shared memory, where the
-// MMA reads it back together with a 128-row activation tile.  For a problem with few rows that is bound by shared-memory
-// bandwidth: per 128 K it writes 32 KB of weights and 32 KB of activations and the MMAs read 64 KB, 128 KB at 128 bytes
-// per clock = 0.54 us, whatever the number of real rows (measured: gate+up 2560 -> 18432 takes 16.4 us from M=33 to
-// M=128, with every role of the kernel idle half of the time).
+// MMA reads it back together with a 128-row activation tile.  For a problem with few rows that costs, per 128 K, 32 KB of
+// weights and 32 KB of activations written to shared memory and 64 KB read by the MMAs, four 4-byte shared-memory stores
+// per packed word on top of the dequant arithmetic, and MMAs of 128 rows whatever the number of real ones (measured:
+// gate+up 2560 -> 18432 takes 16.4 us from M=33 to M=128, 0.55 us per 128 K, with every role idle half of the time).
 // Here the GEMM is issued transposed, C^T[n, m] = W^T[n, k] * X^T[k, m]:
 //  * the 128 weight columns of a tile are the M = 128 rows of the MMA, one per TMEM lane, and the dequant warps write
 //    them straight into tensor memory with tcgen05.st (bf16 pairs of consecutive K per 32-bit cell); they never

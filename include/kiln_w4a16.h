@@ -234,9 +234,11 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
  * Follows kiln_w4a16_set_decode_override.  No counterpart in the reference. */
 void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]);
 
-/* Tuning hook: the M at and above which the tcgen05 prefill kernel is used.  <= 0 restores the
- * built-in rule (M >= 33; M >= 17 for projections of 1025..3072 columns whose activation matrix is at least 128 KB; M > 256
- * for projections of at most 1024 columns); a huge value disables that kernel, 1 forces it. */
+/* Tuning hook: the M at and above which the tcgen05 kernels are used.  <= 0 restores the
+ * built-in rule (M > 256 for projections of at most 1024 columns; otherwise M >= 17 for a plain GEMM with grouped scales,
+ * which the small-batch kernel takes up to 128 rows; with per-column scales or fused epilogue options M >= 33, or M >= 17
+ * for projections of 1025..3072 columns whose activation matrix is at least 128 KB); a huge value disables those kernels,
+ * 1 forces them. */
 void kiln_w4a16_set_prefill_min_m(int min_m);
 
 /* Tuning hook for sweeps: force the tcgen05 kernel's tiling: bn = 128 or 256 columns per tile, K splits (1..8, fp32

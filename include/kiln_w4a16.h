@@ -235,8 +235,8 @@ void kiln_w4a16_set_decode_override(int cluster_k, int warps_k, int warps_n);
 void kiln_w4a16_decode_plan(int m, int n, int k, int out[4]);
 
 /* Tuning hook: the M at and above which the tcgen05 kernels are used.  <= 0 restores the
- * built-in rule (M > 256 for projections of at most 1024 columns; otherwise M >= 17 for a plain GEMM with grouped scales,
- * which the small-batch kernel takes up to 128 rows; with per-column scales or fused epilogue options M >= 33, or M >= 17
+ * built-in rule (M > 256 for projections of at most 1024 columns; otherwise M >= 17 for a plain GEMM,
+ * which the small-batch kernel takes up to 128 rows; with fused epilogue options M >= 33, or M >= 17
  * for projections of 1025..3072 columns whose activation matrix is at least 128 KB); a huge value disables those kernels,
  * 1 forces them. */
 void kiln_w4a16_set_prefill_min_m(int min_m);

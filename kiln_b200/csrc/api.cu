@@ -83,7 +83,7 @@ static int validate(const GemmArgs &a) {
 //    provided the activation matrix is at least 128 KB (smaller ones were measured 40 % slower through its TMA loads);
 //  * projections of 1024 columns or fewer (k, v: four to eight tiles) stay on the decode kernel up to M = 256
 //    (k at M=128: 6.4 / 15.3).
-//  * a GEMM without epilogue options, grouped scales and at most 128 rows runs on the tcgen05 kernel that keeps the
+//  * a GEMM without epilogue options and at most 128 rows runs on the tcgen05 kernel that keeps the
 //    weights in tensor memory (smallm_w4a16_tmem.cu), which moves the crossover to 17 rows for every projection of more
 //    than 1024 columns (M=17: q 7.8 / 6.8, gate+up 18.3 / 13.6, down 12.8 / 10.1, GDN-in 11.0 / 10.0, o 9.1 / 7.0;
 //    M=16, one block of the decode kernel: q 5.7 / 6.6, gate+up 12.0 / 13.4).

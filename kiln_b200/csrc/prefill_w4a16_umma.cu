@@ -995,7 +995,8 @@ int launch_prefill(const GemmArgs &a) {
             if (blocks > cap) blocks = cap;
             note_launch();
             rc = record_cuda_error(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), a.stream, static_cast<float *>(a.workspace),
-                                              static_cast<__nv_bfloat16 *>(a.C), static_cast<const __half *>(a.S), a.m, a.n, c.splits, 0));
+                                              static_cast<__nv_bfloat16 *>(a.C), static_cast<const __half *>(a.S), a.m, a.n, c.splits,
+                                              a.groupsize == -1 ? 1 : 0));
         }
         return rc;
     }

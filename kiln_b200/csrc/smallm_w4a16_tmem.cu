@@ -20,7 +20,8 @@
 // Roles (480 threads): warp 0 TMA producer, warps 1 and 14 MMA issuers (each issues four of the eight K=16 MMAs of a
 // stage into an accumulator of its own: one thread issues about one tcgen05.mma per 105 cycles), warps 2-5 epilogue,
 // warps 6-13 dequant in two teams of four warps (a team covers the four lane quarters) that take the stages in turn.
-// Every wait is bounded (w4a16_async.cuh); K splits write fp32 slabs that splitk_reduce_kernel sums.
+// Every wait is bounded (w4a16_async.cuh); K splits write fp32 slabs that splitk_reduce_kernel sums.  Per-column scales
+// (group size -1): the weights are dequantised unscaled and the scale multiplies the finished sums.
 #include "w4a16_common.cuh"
 #include "w4a16_umma.cuh"
 
@@ -51,6 +52,7 @@ struct SmallMParams {
     float *partial;  // fp32 [splits][m][n] when splits > 1
     uint32_t *status;
     int m, n, n_tiles, splits, k_stages, npad;
+    int per_column;  // one fp16 scale per column (group size -1): dequantised unscaled, the scale applied to the sums
     unsigned long long wait_limit_ns;
 };
 
@@ -216,6 +218,8 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
             tc_fence_after();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kAccBase + acc * 2 * R;
             const size_t col = static_cast<size_t>(nt) * kTileCols + col_in_tile;
+            // per-column scales: applied here when the tile is complete, by the split-K reduction otherwise
+            const float cs = (p.per_column && p.splits == 1) ? __half2float(p.S[scale_single_pos(static_cast<int>(col))]) : 1.f;
             for (int r0 = 0; r0 < p.npad; r0 += 16) {
                 uint32_t a[16], b[16];
                 tmem_ld_32x32b_x16(t0 + r0, a);
@@ -225,7 +229,8 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         if (r0 + i < p.m)
-                            p.C[static_cast<size_t>(r0 + i) * p.n + col] = __float2bfloat16_rn(__uint_as_float(a[i]) + __uint_as_float(b[i]));
+                            p.C[static_cast<size_t>(r0 + i) * p.n + col] =
+                                __float2bfloat16_rn((__uint_as_float(a[i]) + __uint_as_float(b[i])) * cs);
                 } else {
                     float *dst = p.partial + static_cast<size_t>(sp) * p.m * p.n + col;
 #pragma unroll
@@ -266,7 +271,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
             auto load_stage = [&](uint2 (&d)[8], uint32_t &sc, int ks) {
 #pragma unroll
                 for (int kt = 0; kt < 8; ++kt) d[kt] = ld_stream_v2(wbase + static_cast<size_t>(ks * 8 + kt) * chunks_n * 64);
-                sc = ld_stream_u16(sbase + static_cast<size_t>(ks) * p.n);
+                sc = p.per_column ? 0x3C00u : ld_stream_u16(sbase + static_cast<size_t>(ks) * p.n);  // (fp16 1.0)
             };
             // this team's stages of the unit: those whose running stage number is congruent to `team`
             const int kf = ks0 + static_cast<int>((static_cast<uint32_t>(team) + kTeams - it_base % kTeams) % kTeams);
@@ -347,7 +352,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
 
 // Shapes this kernel takes (any row count up to 128 works; the dispatcher decides from which one it pays).
 bool smallm_supported(int m, int n, int k, int groupsize) {
-    return m >= 1 && m <= kMaxRows && groupsize == 128 && n % kTileCols == 0 && k % kStageK == 0;
+    return m >= 1 && m <= kMaxRows && (groupsize == 128 || groupsize == -1) && n % kTileCols == 0 && k % kStageK == 0;
 }
 
 // C = A * dequant(B) with `splits` K splits (fp32 slabs of m * n in `partial` when splits > 1, summed by the caller).
@@ -381,6 +386,7 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     p.splits = splits;
     p.k_stages = a.k / kStageK;
     p.npad = npad;
+    p.per_column = a.groupsize == -1;
     p.wait_limit_ns = current_wait_limit_ns();
 
     static bool attr_set[64] = {};

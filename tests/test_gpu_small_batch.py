@@ -25,19 +25,19 @@ def _restore_hooks():
     _lib.lib().kiln_w4a16_set_small_batch_kernel(1)
 
 
-def _case(m, k, n, seed, device):
-    a, q, s = oracle.synth_inputs(m, k, n, seed=seed, groupsize=128)
-    packed, sp = kiln_b200.pack.repack(q, s, 128)
+def _case(m, k, n, seed, device, groupsize=128):
+    a, q, s = oracle.synth_inputs(m, k, n, seed=seed, groupsize=groupsize)
+    packed, sp = kiln_b200.pack.repack(q, s, groupsize)
     return dict(a=a, q=q, s=s, a_t=to_torch_bf16(a, device), b_t=torch.from_numpy(packed).to(device),
                 s_t=torch.from_numpy(sp.view(np.int16).copy()).view(torch.float16).to(device))
 
 
-def _run(case, small_batch, m, n, device):
+def _run(case, small_batch, m, n, device, groupsize=128):
     lib = _lib.lib()
     lib.kiln_w4a16_set_prefill_min_m(1)  # a tcgen05 kernel whatever the built-in rule says
     lib.kiln_w4a16_set_small_batch_kernel(1 if small_batch else 0)
     buf = torch.full((m + 2, n), 3.0, dtype=torch.bfloat16, device=device)
-    out = kiln_b200.marlin_w4a16_gemm(case["a_t"], case["b_t"], case["s_t"], 128, out=buf[1:m + 1])
+    out = kiln_b200.marlin_w4a16_gemm(case["a_t"], case["b_t"], case["s_t"], groupsize, out=buf[1:m + 1])
     torch.cuda.synchronize()
     assert lib.kiln_w4a16_check_device_status(None, None) == 0, "a bounded device wait gave up"
     assert (buf[0] == 3.0).all() and (buf[m + 1] == 3.0).all()  # rows outside [0, m) untouched
@@ -61,6 +61,16 @@ def test_small_batch_kernel_matches_the_oracle_and_the_general_kernel(cuda_devic
     full = case["a_t"].float() @ w
     assert float((out.float() - full).abs().max() / full.abs().max()) <= REL_TOL
     general = _run(case, False, m, n, cuda_device)
+    assert torch.equal(out.view(torch.int16), general.view(torch.int16)), "differs from the general tcgen05 kernel"
+
+
+# per-column scales (group size -1): dequantised unscaled, the scale applied by the epilogue or by the split-K reduction
+@pytest.mark.parametrize("m,k,n", [(24, 640, 512), (100, 2560, 4096), (64, 9216, 2560)])
+def test_small_batch_kernel_with_per_column_scales(cuda_device, m, k, n):
+    case = _case(m, k, n, seed=m + k + n, device=cuda_device, groupsize=-1)
+    out = _run(case, True, m, n, cuda_device, groupsize=-1)
+    assert rel_err(from_torch_bf16(out), C.gemm_fp64(case["a"], case["q"], case["s"], -1)) <= REL_TOL
+    general = _run(case, False, m, n, cuda_device, groupsize=-1)
     assert torch.equal(out.view(torch.int16), general.view(torch.int16)), "differs from the general tcgen05 kernel"
 
 

@@ -197,12 +197,17 @@ int validate_epilogue(const kiln_w4a16_epilogue_t *ep, int n) {
 }
 }  // namespace
 
+// SwiGLU alone, fused by the tcgen05 kernel that would run it: the kernel choice is the plain GEMM's (from 17 rows)
+static bool ex_plain(const kiln_w4a16_epilogue_t *ep, int m, int n, int k) {
+    return ep->lora_rank == 0 && ep->swiglu && m <= 128 && prefill_fuses_swiglu(m, n, k);
+}
+
 size_t kiln_w4a16_workspace_bytes_ex(int m, int n, int k, const kiln_w4a16_epilogue_t *ep) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
     const bool opts = ep && (ep->swiglu || ep->lora_rank);
     if (!opts) return kiln_w4a16_workspace_bytes(m, n, k);
     size_t need = align256(static_cast<size_t>(m) * ep->lora_rank * sizeof(float));
-    if (use_prefill(m, n, k, 128)) {
+    if (use_prefill(m, n, k, 128, ex_plain(ep, m, n, k))) {
         // tcgen05 kernel: SwiGLU is fused when the tiling writes whole tiles, the LoRA delta whenever the scales are grouped
         // (this call does not know the group size, so it reserves the composed path's buffer whenever there is a delta);
         // what is not fused is applied by a second pass over the bf16 GEMM result kept in the workspace
@@ -225,7 +230,7 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16_ex(const void *A, const void *B, void *
     const size_t need = kiln_w4a16_workspace_bytes_ex(m, n, k, ep);
     if (need > 0 && (!workspace || workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
-    const bool tc = use_prefill(m, n, k, groupsize);
+    const bool tc = use_prefill(m, n, k, groupsize, ex_plain(ep, m, n, k));
     const bool fuse_lora = tc && ep->lora_rank && prefill_fuses_lora(groupsize, ep->lora_rank);
     const bool fuse_swiglu = tc && ep->swiglu && prefill_fuses_swiglu(m, n, k);
     void *t = nullptr;

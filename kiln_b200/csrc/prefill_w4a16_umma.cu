@@ -932,8 +932,15 @@ int launch_bn(const CUtensorMap &tmap, const CUtensorMap &tmap_c, PrefillParams 
 }  // namespace
 
 // SwiGLU can be fused into the tcgen05 kernel's epilogue when its tiling for the problem writes whole tiles as bf16.
+// whether the small-batch kernel runs a plain problem that the planner tiled as `c`
+static bool smallm_takes(const PrefillConfig &c, int m, int n, int k, int groupsize) {
+    return g_smallm_enabled && g_test_drop_a_load < 0 && c.bn == 128 && c.mt == 1 && !c.stream_k && c.splits <= k / 128 &&
+           smallm_supported(m, n, k, groupsize);
+}
+
 bool prefill_fuses_swiglu(int m, int n, int k) {
     const PrefillConfig c = choose_prefill(m, n, k);
+    if (c.splits == 1 && smallm_takes(c, m, n, k, 128)) return true;  // (its epilogue pairs the gate and up warps)
     // (not the 128-column tiles of one M-tile: their two K-parity accumulators would have to be added first, and at those
     // batch sizes a second pass over the small output costs less than a longer epilogue)
     return c.splits == 1 && !c.stream_k && !(c.bn == 128 && c.mt == 1);
@@ -979,12 +986,12 @@ int launch_prefill(const GemmArgs &a) {
     if (!status) return KILN_W4A16_ERR_CUDA;
     const bool fused = a.n_peers > 0 || a.mc_c;  // the peer-store epilogue needs whole tiles: no split-K, no stream-K
     const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused && !a.no_scratch);
-    if (a.swiglu && (fused || c.splits != 1 || c.stream_k || (c.bn == 128 && c.mt == 1)))
-        return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_swiglu first)
     // At most 128 rows in 128-column tiles: the kernel that keeps the dequantised weights in tensor memory (same tiling,
     // same K splits and workspace, so everything the planner reports holds for it too)
-    if (g_smallm_enabled && !fused && !a.swiglu && a.lora_r == 0 && g_test_drop_a_load < 0 && c.bn == 128 && c.mt == 1 &&
-        !c.stream_k && c.splits <= a.k / 128 && smallm_supported(a.m, a.n, a.k, a.groupsize)) {
+    const bool smallm = smallm_takes(c, a.m, a.n, a.k, a.groupsize) && !fused && a.lora_r == 0 && (!a.swiglu || c.splits == 1);
+    if (!smallm && a.swiglu && (fused || c.splits != 1 || c.stream_k || (c.bn == 128 && c.mt == 1)))
+        return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_swiglu first)
+    if (smallm) {
         const size_t need = workspace_for(c, a.m, a.n);
         if (need > 0 && (!a.workspace || a.workspace_bytes < need)) return KILN_W4A16_ERR_WORKSPACE;
         int rc = launch_smallm(a, c.splits, static_cast<float *>(a.workspace));

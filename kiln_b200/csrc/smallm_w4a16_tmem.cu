@@ -20,6 +20,8 @@
 // Roles (480 threads): warp 0 TMA producer, warps 1 and 14 MMA issuers (each issues four of the eight K=16 MMAs of a
 // stage into an accumulator of its own: one thread issues about one tcgen05.mma per 105 cycles), warps 2-5 epilogue,
 // warps 6-13 dequant in two teams of four warps (a team covers the four lane quarters) that take the stages in turn.
+// SwiGLU (gate and up columns interleaved in runs of 32, no K split): the warp that owns a run of up columns passes its sums
+// to the warp that owns the gate columns through shared memory, which writes silu(gate) * up.
 // Every wait is bounded (w4a16_async.cuh); K splits write fp32 slabs that splitk_reduce_kernel sums.  Per-column scales
 // (group size -1): the weights are dequantised unscaled and the scale multiplies the finished sums.
 #include "w4a16_common.cuh"
@@ -43,7 +45,9 @@ constexpr int kIssuerWarp2 = kDequantWarp0 + kTeamWarps * kTeams;
 constexpr int kThreads = (kIssuerWarp2 + 1) * 32;
 constexpr int kBarrierBytes = 256;
 template <int R>
-constexpr int smem_bytes() { return kStages * 2 * R * 128 + kBarrierBytes + 1024; }  // + alignment slack
+constexpr int smem_bytes() {  // stages, barriers, the SwiGLU exchange area (two warp pairs x gate and up x R rows x 32 floats), alignment slack
+    return kStages * 2 * R * 128 + kBarrierBytes + 4 * R * 32 * 4 + 1024;
+}
 
 struct SmallMParams {
     const uint2 *B;  // packed weights seen as 8-byte halves of the 16-byte lane pieces
@@ -52,6 +56,7 @@ struct SmallMParams {
     float *partial;  // fp32 [splits][m][n] when splits > 1
     uint32_t *status;
     int m, n, n_tiles, splits, k_stages, npad;
+    int swiglu;      // columns hold gate and up interleaved in runs of 32; C is [m, n/2] = silu(gate) * up (splits == 1 only)
     int per_column;  // one fp16 scale per column (group size -1): dequantised unscaled, the scale applied to the sums
     unsigned long long wait_limit_ns;
 };
@@ -220,6 +225,33 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
             const size_t col = static_cast<size_t>(nt) * kTileCols + col_in_tile;
             // per-column scales: applied here when the tile is complete, by the split-K reduction otherwise
             const float cs = (p.per_column && p.splits == 1) ? __half2float(p.S[scale_single_pos(static_cast<int>(col))]) : 1.f;
+            if (p.swiglu) {
+                // A 64-column chunk is a run of 32 gate columns and the 32 up columns that go with them: this warp owns
+                // one run, the warp of the neighbouring lane quarter the other, column for column in the same lanes.
+                // Both put their sums into shared memory, then each computes silu(gate) * up for half of the rows.
+                const int hf = quarter & 1, ch = quarter >> 1;
+                float *xg = reinterpret_cast<float *>(bar_gen + kBarrierBytes) + ch * (2 * R * 32), *xu = xg + R * 32;
+                float *mine = hf ? xu : xg;
+                for (int r0 = 0; r0 < p.npad; r0 += 16) {
+                    uint32_t a[16], b[16];
+                    tmem_ld_32x32b_x16(t0 + r0, a);
+                    tmem_ld_32x32b_x16(t0 + R + r0, b);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) mine[(r0 + i) * 32 + lane] = (__uint_as_float(a[i]) + __uint_as_float(b[i])) * cs;
+                }
+                // (both warps of a pair come here after the same mbarrier wait above, and leave together)
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + ch) : "memory");
+                // (a lane holds the same column of its run in both warps: col_in_tile % 32)
+                const size_t ocol = static_cast<size_t>(nt) * (kTileCols / 2) + ch * 32 + (col_in_tile & 31);
+                const int half = p.npad >> 1, r_end = min(p.m, (hf + 1) * half);
+#pragma unroll 4
+                for (int r = hf * half; r < r_end; ++r) {
+                    const float g = xg[r * 32 + lane], u = xu[r * 32 + lane];
+                    p.C[static_cast<size_t>(r) * (p.n >> 1) + ocol] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+                }
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + ch) : "memory");  // the exchange area may be written again
+            } else
             for (int r0 = 0; r0 < p.npad; r0 += 16) {
                 uint32_t a[16], b[16];
                 tmem_ld_32x32b_x16(t0 + r0, a);
@@ -361,7 +393,7 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     if (!enc) return KILN_W4A16_ERR_CUDA;
     uint32_t *status = device_status_word();
     if (!status) return KILN_W4A16_ERR_CUDA;
-    if (splits < 1 || splits > a.k / kStageK || (splits > 1 && !partial)) return KILN_W4A16_ERR_KERN_SHAPE;
+    if (splits < 1 || splits > a.k / kStageK || (splits > 1 && !partial) || (a.swiglu && splits != 1)) return KILN_W4A16_ERR_KERN_SHAPE;
 
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.k), static_cast<cuuint64_t>(a.m)};
@@ -387,6 +419,7 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     p.k_stages = a.k / kStageK;
     p.npad = npad;
     p.per_column = a.groupsize == -1;
+    p.swiglu = a.swiglu;
     p.wait_limit_ns = current_wait_limit_ns();
 
     static bool attr_set[64] = {};

@@ -46,10 +46,12 @@ def test_swiglu_fused_into_the_gate_up_gemm(cuda_device, m, k, n_half):
     assert rel_err(from_torch_bf16(out), (_silu(g) * u).astype(np.float32)) <= REL_TOL
 
 
-@pytest.mark.parametrize("m,k,n_half,fused_expected", [(64, 2560, 9216, False), (384, 512, 2048, False), (300, 2560, 9216, True),
+@pytest.mark.parametrize("m,k,n_half,fused_expected", [(64, 2560, 9216, True), (24, 2560, 9216, True), (128, 2560, 9216, True),
+                                                        (48, 2560, 2048, False), (384, 512, 2048, False), (300, 2560, 9216, True),
                                                         (600, 1152, 4096, True), (2048, 640, 1024, True)])
 def test_swiglu_at_the_batch_sizes_of_the_tcgen05_kernel(cuda_device, m, k, n_half, fused_expected):
-    """Batch sizes of the tcgen05 kernel: tilings that write whole tiles from one accumulator per M-tile compute
+    """Batch sizes of the tcgen05 kernels: the small-batch kernel without a K split (its gate and up warps meet through
+    shared memory) and the general kernel's tilings that write whole tiles from one accumulator per M-tile compute
     silu(gate) * up in the epilogue (no workspace needed); the others compose the GEMM with a second pass.  Rows outside
     [0, m) stay untouched."""
     import ctypes

@@ -103,3 +103,24 @@ def test_small_batch_kernel_with_extreme_nibbles_and_scales(cuda_device):
                 s_t=torch.from_numpy(sp.view(np.int16).copy()).view(torch.float16).to(cuda_device))
     out = _run(case, True, m, n, cuda_device)
     assert rel_err(from_torch_bf16(out), C.gemm_fp64(a, q, s, 128)) <= REL_TOL
+
+
+def test_swiglu_is_fused_from_17_rows_under_the_built_in_rule(cuda_device):
+    """gate+up with SwiGLU at 24 rows: no hook, no workspace, one launch of the small-batch kernel (the decode kernel below
+    17 rows, which fuses it too)."""
+    import ctypes
+
+    from tests.test_gpu_epilogue import _gate_up_case, _silu
+
+    lib = _lib.lib()
+    ep = _lib.Epilogue()
+    ep.swiglu = 1
+    for m in (16, 24):
+        assert int(lib.kiln_w4a16_workspace_bytes_ex(m, 18432, 2560, ctypes.byref(ep))) == 0
+        a, fused, g, u = _gate_up_case(m, 2560, 9216, seed=40 + m, dev=cuda_device)
+        before = lib.kiln_w4a16_launch_count()
+        out = kiln_b200.swiglu_gate_up(to_torch_bf16(a, cuda_device), fused)
+        torch.cuda.synchronize()
+        assert lib.kiln_w4a16_check_device_status(None, None) == 0
+        assert lib.kiln_w4a16_launch_count() - before == 1
+        assert rel_err(from_torch_bf16(out), (_silu(g) * u).astype(np.float32)) <= REL_TOL

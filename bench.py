@@ -320,6 +320,18 @@ def fused_rows_detail(d: Device, peaks):
         us = d.time_graph(fn2, nl, reps=7)
         by = alg_bytes(m, k, 18432) - m * 9216 * 2
         out[f"gate_up_swiglu:m{m}"] = {"us": round(us, 2), "GBps": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4)}
+    for m in (24, 64):  # continuous-batching row counts: SwiGLU fused into the small-batch tcgen05 kernel's epilogue
+        a = d.acts(m, k)
+        o2 = t.empty((m, 9216), dtype=t.bfloat16, device=d.dev)
+        nl = 28
+
+        def fn3():
+            for i in range(nl):
+                kiln_b200.swiglu_gate_up(a, gu[i % gu_copies], out=o2)
+
+        us = d.time_graph(fn3, nl, reps=5)
+        by = alg_bytes(m, k, 18432) - m * 9216 * 2
+        out[f"gate_up_swiglu:m{m}"] = {"us": round(us, 2), "GBps": round(by / us / 1e3, 1), "frac_hbm": round(by / us / 1e3 / peaks["hbm_gbs"], 4)}
     return out
 
 

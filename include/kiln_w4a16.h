@@ -75,8 +75,9 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
  *             unrounded sums (the reference rounds gate and up to bf16 first).  lora_b follows the same column order.
  * For batch sizes the decode kernel serves the options are fused into that kernel's final reduction.  For larger ones
  * the LoRA delta rides in the tcgen05 kernel as extra K-steps (grouped scales; t is then written as bf16), and SwiGLU is
- * fused into its epilogue whenever the tiling writes whole tiles from one accumulator per M-tile; what is not fused is
- * applied by a second kernel to the bf16 GEMM result kept in the workspace. */
+ * fused into the epilogue of the small-batch kernel (up to 128 rows, K not split) and of the general kernel's tilings
+ * that write whole tiles from one accumulator per M-tile; what is not fused is applied by a second kernel to the bf16
+ * GEMM result kept in the workspace. */
 typedef struct kiln_w4a16_epilogue {
     int swiglu;
     const void *lora_a;

@@ -44,9 +44,9 @@ constexpr int kDequantWarp0 = 6, kTeamWarps = 4, kTeams = 2;
 constexpr int kIssuerWarp2 = kDequantWarp0 + kTeamWarps * kTeams;
 constexpr int kThreads = (kIssuerWarp2 + 1) * 32;
 constexpr int kBarrierBytes = 256;
-template <int R>
+template <int R, bool SWIGLU>
 constexpr int smem_bytes() {  // stages, barriers, the SwiGLU exchange area (two warp pairs x gate and up x R rows x 32 floats), alignment slack
-    return kStages * 2 * R * 128 + kBarrierBytes + 4 * R * 32 * 4 + 1024;
+    return kStages * 2 * R * 128 + kBarrierBytes + (SWIGLU ? 4 * R * 32 * 4 : 0) + 1024;
 }
 
 struct SmallMParams {
@@ -89,6 +89,13 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
+// named barrier of the two epilogue warps that share a 64-column chunk (ids 1 and 2; 0 is __syncthreads)
+__device__ __forceinline__ void pair_barrier(int ch) {
+    if (ch == 0)
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+    else
+        asm volatile("bar.sync 2, 64;" ::: "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]: A = 128 lanes x 8 cells (16 K as bf16 pairs), B = K-major tile of N rows
 __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                  uint32_t accumulate) {
@@ -100,7 +107,9 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t d_tmem, uint32_t a_tme
         : "memory");
 }
 
-template <int R>
+// SWIGLU is a template parameter so that the plain kernel's epilogue is compiled on its own (with the option as a run-time
+// branch the plain epilogue came out 6-27 % slower for 64-128 rows).
+template <int R, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMParams p) {
     constexpr int kXAtomBytes = R * 128, kXStageBytes = 2 * kXAtomBytes;
@@ -225,7 +234,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
             const size_t col = static_cast<size_t>(nt) * kTileCols + col_in_tile;
             // per-column scales: applied here when the tile is complete, by the split-K reduction otherwise
             const float cs = (p.per_column && p.splits == 1) ? __half2float(p.S[scale_single_pos(static_cast<int>(col))]) : 1.f;
-            if (p.swiglu) {
+            if constexpr (SWIGLU) {
                 // A 64-column chunk is a run of 32 gate columns and the 32 up columns that go with them: this warp owns
                 // one run, the warp of the neighbouring lane quarter the other, column for column in the same lanes.
                 // Both put their sums into shared memory, then each computes silu(gate) * up for half of the rows.
@@ -241,7 +250,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
                     for (int i = 0; i < 16; ++i) mine[(r0 + i) * 32 + lane] = (__uint_as_float(a[i]) + __uint_as_float(b[i])) * cs;
                 }
                 // (both warps of a pair come here after the same mbarrier wait above, and leave together)
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + ch) : "memory");
+                pair_barrier(ch);
                 // (a lane holds the same column of its run in both warps: col_in_tile % 32)
                 const size_t ocol = static_cast<size_t>(nt) * (kTileCols / 2) + ch * 32 + (col_in_tile & 31);
                 const int half = p.npad >> 1, r_end = min(p.m, (hf + 1) * half);
@@ -250,7 +259,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
                     const float g = xg[r * 32 + lane], u = xu[r * 32 + lane];
                     p.C[static_cast<size_t>(r) * (p.n >> 1) + ocol] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
                 }
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + ch) : "memory");  // the exchange area may be written again
+                pair_barrier(ch);  // the exchange area may be written again
             } else
             for (int r0 = 0; r0 < p.npad; r0 += 16) {
                 uint32_t a[16], b[16];
@@ -422,28 +431,31 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     p.swiglu = a.swiglu;
     p.wait_limit_ns = current_wait_limit_ns();
 
-    static bool attr_set[64] = {};
+    static bool attr_set[4][64] = {};  // per kernel variant and device: the shared-memory attribute is set once
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 64 && !attr_set[dev]) {
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_smallm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<64>())))
-            return rc;
-        if (int rc = record_cuda_error(cudaFuncSetAttribute(w4a16_smallm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<128>())))
-            return rc;
-        attr_set[dev] = true;
-    }
-    const int units = p.n_tiles * p.splits;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(units < device_sm_count() ? units : device_sm_count());
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = a.m <= 64 ? smem_bytes<64>() : smem_bytes<128>();
-    cfg.stream = a.stream;
-    cudaLaunchAttribute attr = pdl_attribute();
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    note_launch();
-    return record_cuda_error(a.m <= 64 ? cudaLaunchKernelEx(&cfg, w4a16_smallm_kernel<64>, tmap, p)
-                                       : cudaLaunchKernelEx(&cfg, w4a16_smallm_kernel<128>, tmap, p));
+    auto launch = [&](auto kernel, int smem, int variant) -> int {
+        if (dev < 64 && !attr_set[variant][dev]) {
+            if (int rc = record_cuda_error(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return rc;
+            attr_set[variant][dev] = true;
+        }
+        const int units = p.n_tiles * p.splits;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(units < device_sm_count() ? units : device_sm_count());
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = a.stream;
+        cudaLaunchAttribute attr = pdl_attribute();
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        note_launch();
+        return record_cuda_error(cudaLaunchKernelEx(&cfg, kernel, tmap, p));
+    };
+    if (a.swiglu)
+        return a.m <= 64 ? launch(w4a16_smallm_kernel<64, true>, smem_bytes<64, true>(), 2)
+                         : launch(w4a16_smallm_kernel<128, true>, smem_bytes<128, true>(), 3);
+    return a.m <= 64 ? launch(w4a16_smallm_kernel<64, false>, smem_bytes<64, false>(), 0)
+                     : launch(w4a16_smallm_kernel<128, false>, smem_bytes<128, false>(), 1);
 }
 
 }  // namespace kiln

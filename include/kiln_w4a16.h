@@ -74,7 +74,7 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
  *             same indices; n = 2 * intermediate size).  C is then [m, n/2] = silu(gate) * up, computed in fp32 from the
  *             unrounded sums (the reference rounds gate and up to bf16 first).  lora_b follows the same column order.
  * For batch sizes the decode kernel serves the options are fused into that kernel's final reduction.  For larger ones
- * the LoRA delta rides in the tcgen05 kernel as extra K-steps (grouped scales; t is then written as bf16), and SwiGLU is
+ * the LoRA delta rides in the tcgen05 kernels as extra K-steps (grouped scales; t is then written as bf16), and SwiGLU is
  * fused into the epilogue of the small-batch kernel (up to 128 rows, K not split) and of the general kernel's tilings
  * that write whole tiles from one accumulator per M-tile; what is not fused is applied by a second kernel to the bf16
  * GEMM result kept in the workspace. */

@@ -988,7 +988,8 @@ int launch_prefill(const GemmArgs &a) {
     const PrefillConfig c = choose_prefill(a.m, a.n, a.k, true, !fused && !a.no_scratch);
     // At most 128 rows in 128-column tiles: the kernel that keeps the dequantised weights in tensor memory (same tiling,
     // same K splits and workspace, so everything the planner reports holds for it too)
-    const bool smallm = smallm_takes(c, a.m, a.n, a.k, a.groupsize) && !fused && a.lora_r == 0 && (!a.swiglu || c.splits == 1);
+    const bool smallm = smallm_takes(c, a.m, a.n, a.k, a.groupsize) && !fused && (!a.swiglu || c.splits == 1) &&
+                        (a.lora_r == 0 || (a.lora_t && a.lora_b && prefill_fuses_lora(a.groupsize, a.lora_r)));
     if (!smallm && a.swiglu && (fused || c.splits != 1 || c.stream_k || (c.bn == 128 && c.mt == 1)))
         return KILN_W4A16_ERR_KERN_SHAPE;  // (callers ask prefill_fuses_swiglu first)
     if (smallm) {

@@ -22,6 +22,8 @@
 // warps 6-13 dequant in two teams of four warps (a team covers the four lane quarters) that take the stages in turn.
 // SwiGLU (gate and up columns interleaved in runs of 32, no K split): the warp that owns a run of up columns passes its sums
 // to the warp that owns the gate columns through shared memory, which writes silu(gate) * up.
+// LoRA delta (grouped scales): one extra stage at the start of a tile's K range, its tensor-memory operand the tile's rows of
+// lora_b and its activation tile t = scale * x * A^T (bf16, written by the kernel launched just before).
 // Every wait is bounded (w4a16_async.cuh); K splits write fp32 slabs that splitk_reduce_kernel sums.  Per-column scales
 // (group size -1): the weights are dequantised unscaled and the scale multiplies the finished sums.
 #include "w4a16_common.cuh"
@@ -56,6 +58,11 @@ struct SmallMParams {
     float *partial;  // fp32 [splits][m][n] when splits > 1
     uint32_t *status;
     int m, n, n_tiles, splits, k_stages, npad;
+    // LoRA delta C += t * lora_b^T: t = scale * x * A^T is bf16 [m, lora_r] (its tensor map is the kernel's second), lora_b
+    // bf16 [n, lora_r], lora_r a multiple of 8 up to 128.  The unit that starts a tile's K range begins with one extra
+    // stage whose tensor-memory operand is the tile's rows of lora_b and whose activation tile is t.
+    const __nv_bfloat16 *lora_b;
+    int lora_r;
     int swiglu;      // columns hold gate and up interleaved in runs of 32; C is [m, n/2] = silu(gate) * up (splits == 1 only)
     int per_column;  // one fp16 scale per column (group size -1): dequantised unscaled, the scale applied to the sums
     unsigned long long wait_limit_ns;
@@ -111,7 +118,7 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t d_tmem, uint32_t a_tme
 // branch the plain epilogue came out 6-27 % slower for 64-128 rows).
 template <int R, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
-w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMParams p) {
+w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t, const SmallMParams p) {
     constexpr int kXAtomBytes = R * 128, kXStageBytes = 2 * kXAtomBytes;
     constexpr int kAccBufs = R == 64 ? 2 : 1;
     extern __shared__ uint8_t smem_raw[];
@@ -164,6 +171,8 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
         ks1 = (sp + 1) * p.k_stages / p.splits;
     };
     int nt, sp, ks0, ks1;
+    // stage "ks0 - 1" of a unit with sp == 0 is the LoRA stage, when there is a delta
+    auto lora_pre = [&](int sp_) { return (p.lora_r > 0 && sp_ == 0) ? 1 : 0; };
 
     if (warp == 0) {
         // ---------------- TMA producer: activations ----------------
@@ -173,13 +182,15 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 unit_range(u, nt, sp, ks0, ks1);
-                for (int ks = ks0; ks < ks1; ++ks, ++it) {
+                for (int ks = ks0 - lora_pre(sp); ks < ks1; ++ks, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0xA00u | s, p.wait_limit_ns))) break;
                     mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(p.npad) * 256u);  // (rows past m are zero-filled and counted)
-                    tma_load_2d(smem_base + s * kXStageBytes, &tmap_x, ks * kStageK, 0, full(s));
-                    tma_load_2d(smem_base + s * kXStageBytes + kXAtomBytes, &tmap_x, ks * kStageK + 64, 0, full(s));
+                    const CUtensorMap *map = ks < ks0 ? &tmap_t : &tmap_x;  // (columns of t past lora_r read zero)
+                    const int x0 = ks < ks0 ? 0 : ks * kStageK;
+                    tma_load_2d(smem_base + s * kXStageBytes, map, x0, 0, full(s));
+                    tma_load_2d(smem_base + s * kXStageBytes + kXAtomBytes, map, x0 + 64, 0, full(s));
                 }
             }
             if (!ok) {  // drain: wait (bounded, ignoring the abort flag) for copies already issued
@@ -199,11 +210,12 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
                 unit_range(u, nt, sp, ks0, ks1);
                 const uint32_t acc = tile % kAccBufs, acc_ph = (tile / kAccBufs) & 1;
                 const uint32_t d_tmem = tmem_base + kAccBase + (acc * 2 + q) * R;
-                for (int ks = ks0; ks < ks1; ++ks, ++it) {
+                const int ksf = ks0 - lora_pre(sp);  // first stage of the unit
+                for (int ks = ksf; ks < ks1; ++ks, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = mbar_wait(full(s), ph, abort_flag, p.status, 0xB00u | s, p.wait_limit_ns))) break;
-                    if (ks == ks0) {  // first write into this accumulator: the epilogue must have drained it
+                    if (ks == ksf) {  // first write into this accumulator: the epilogue must have drained it
                         if (!(ok = mbar_wait(tmem_empty(acc), acc_ph ^ 1, abort_flag, p.status, 0xC00u | acc, p.wait_limit_ns))) break;
                     }
                     tc_fence_after();
@@ -211,7 +223,7 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
                     for (int j = 0; j < 4; ++j) {
                         const int kg = 4 * q + j;  // K=16 slice of the stage: atom q, slice j
                         const uint64_t b_desc = make_smem_desc(smem_base + s * kXStageBytes + q * kXAtomBytes) + 2 * j;
-                        umma_bf16_tmem_a(d_tmem, tmem_base + s * kWStageCols + kg * 8, b_desc, idesc, (ks > ks0 || j > 0) ? 1u : 0u);
+                        umma_bf16_tmem_a(d_tmem, tmem_base + s * kWStageCols + kg * 8, b_desc, idesc, (ks > ksf || j > 0) ? 1u : 0u);
                     }
                     umma_commit(empty(s));
                     if (ks == ks1 - 1) umma_commit(tmem_full(acc));
@@ -314,6 +326,37 @@ w4a16_smallm_kernel(const __grid_constant__ CUtensorMap tmap_x, const SmallMPara
                 for (int kt = 0; kt < 8; ++kt) d[kt] = ld_stream_v2(wbase + static_cast<size_t>(ks * 8 + kt) * chunks_n * 64);
                 sc = p.per_column ? 0x3C00u : ld_stream_u16(sbase + static_cast<size_t>(ks) * p.n);  // (fp16 1.0)
             };
+            if (lora_pre(sp)) {
+                // LoRA stage: the tensor-memory operand is this tile's rows of lora_b, one row per lane, K = lora_r padded
+                // with zeros to 128.  A weight like any other: it is read without waiting for the previous kernel.
+                if (it_base % kTeams == static_cast<uint32_t>(team)) {
+                    const int s = it_base % kStages;
+                    const uint32_t ph = (it_base / kStages) & 1;
+                    const int col_in_tile = 64 * ch + 16 * (2 * hf + (qd >> 1)) + 8 * (qd & 1) + c;
+                    const uint4 *row = reinterpret_cast<const uint4 *>(p.lora_b + (static_cast<size_t>(nt) * kTileCols + col_in_tile) * p.lora_r);
+                    if ((ok = mbar_wait(empty(s), ph ^ 1, abort_flag, p.status, 0xE00u | s, p.wait_limit_ns))) {
+                        tc_fence_after();
+#pragma unroll 1
+                        for (int h = 0; h < 4; ++h) {  // four K tiles of 16 = four pairs of 16-byte pieces at a time (few registers)
+                            uint4 lw[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                lw[i] = 8 * (4 * h + i) + 8 <= p.lora_r ? ld_stream_v4(row + 4 * h + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                            for (int kt = 0; kt < 2; ++kt) {
+                                const uint32_t r[8] = {lw[2 * kt].x, lw[2 * kt].y, lw[2 * kt].z, lw[2 * kt].w,
+                                                       lw[2 * kt + 1].x, lw[2 * kt + 1].y, lw[2 * kt + 1].z, lw[2 * kt + 1].w};
+                                tmem_st_32x32b_x8(t_lane + s * kWStageCols + (2 * h + kt) * 8, r);
+                            }
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(full(s));
+                    }
+                }
+                ++it_base;
+                if (!ok) break;
+            }
             // this team's stages of the unit: those whose running stage number is congruent to `team`
             const int kf = ks0 + static_cast<int>((static_cast<uint32_t>(team) + kTeams - it_base % kTeams) % kTeams);
             // Packed words and scales of the team's next three stages are always in flight, each stage's in registers of
@@ -415,6 +458,17 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return KILN_W4A16_ERR_CUDA;
 
+    CUtensorMap tmap_t = tmap;  // (unused without a LoRA delta)
+    const bool lora = a.lora_r > 0 && a.lora_t && a.lora_b;
+    if (lora) {
+        if (a.groupsize == -1 || a.lora_r % 8 != 0 || a.lora_r > 128) return KILN_W4A16_ERR_KERN_SHAPE;
+        const cuuint64_t td[2] = {static_cast<cuuint64_t>(a.lora_r), static_cast<cuuint64_t>(a.m)};
+        const cuuint64_t ts[1] = {static_cast<cuuint64_t>(a.lora_r) * 2};
+        if (enc(&tmap_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.lora_t), td, ts, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return KILN_W4A16_ERR_CUDA;
+    }
+
     SmallMParams p{};
     p.B = static_cast<const uint2 *>(a.B);
     p.S = static_cast<const __half *>(a.S);
@@ -429,6 +483,8 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
     p.npad = npad;
     p.per_column = a.groupsize == -1;
     p.swiglu = a.swiglu;
+    p.lora_b = lora ? static_cast<const __nv_bfloat16 *>(a.lora_b) : nullptr;
+    p.lora_r = lora ? a.lora_r : 0;
     p.wait_limit_ns = current_wait_limit_ns();
 
     static bool attr_set[4][64] = {};  // per kernel variant and device: the shared-memory attribute is set once
@@ -449,7 +505,7 @@ int launch_smallm(const GemmArgs &a, int splits, float *partial) {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         note_launch();
-        return record_cuda_error(cudaLaunchKernelEx(&cfg, kernel, tmap, p));
+        return record_cuda_error(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_t, p));
     };
     if (a.swiglu)
         return a.m <= 64 ? launch(w4a16_smallm_kernel<64, true>, smem_bytes<64, true>(), 2)

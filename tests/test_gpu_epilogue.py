@@ -96,7 +96,8 @@ def _lora(rng, r, k, n):
 
 
 @pytest.mark.parametrize("r", [8, 20, 64, 128])
-@pytest.mark.parametrize("m,k,n", [(1, 2560, 4096), (16, 2560, 4096), (5, 640, 768), (512, 640, 1024)])
+@pytest.mark.parametrize("m,k,n", [(1, 2560, 4096), (16, 2560, 4096), (5, 640, 768), (512, 640, 1024),
+                                   (40, 2560, 4096), (100, 640, 2560), (128, 4096, 2560)])  # (the last three: small-batch kernel)
 def test_lora_delta_in_the_epilogue(cuda_device, m, k, n, r):
     a, q, s = oracle.synth_inputs(m, k, n, seed=r + m)
     rng = np.random.default_rng(r * 7 + m)
@@ -112,11 +113,12 @@ def test_lora_delta_in_the_epilogue(cuda_device, m, k, n, r):
     assert rel_err(from_torch_bf16(out), (base + delta).astype(np.float32)) <= REL_TOL
 
 
-@pytest.mark.parametrize("m,k,nh", [(3, 640, 512), (300, 640, 512), (300, 1152, 4096)])
+@pytest.mark.parametrize("m,k,nh", [(3, 640, 512), (300, 640, 512), (300, 1152, 4096), (64, 2560, 9216), (48, 640, 2048)])
 def test_lora_and_swiglu_together(cuda_device, m, k, nh):
     """Separate LoRA adapters on gate and up are one adapter of twice the rank on the fused matrix: A = [A_g; A_u],
     B = [[B_g, 0]; [0, B_u]] with its rows in the fused column order.  m = 3: decode kernel; m = 300: tcgen05 kernel with
-    the delta as extra K-steps, SwiGLU composed (narrow tiles) or in the epilogue (pairs of 256-column tiles)."""
+    the delta as extra K-steps, SwiGLU composed (narrow tiles) or in the epilogue (pairs of 256-column tiles); m = 64 and
+    48: small-batch kernel, the delta as an extra stage and SwiGLU in its epilogue (or composed when K is split)."""
     r = 8
     a, fused, g, u = _gate_up_case(m, k, nh, seed=99, dev=cuda_device)
     rng = np.random.default_rng(5)

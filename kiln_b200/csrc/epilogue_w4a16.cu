@@ -43,28 +43,34 @@ __global__ void __launch_bounds__(256) lora_down_kernel(const __nv_bfloat16 *__r
 }
 
 // The same for larger batches: a CTA takes eight rows of x, so that every adapter row it reads serves eight dot products
-// (the kernel above re-reads the whole adapter once per row of x).  grid = (ceil(r / 8), ceil(m / 8)), block = 256.
+// (the kernel above re-reads the whole adapter once per row of x), and two adapter rows, each split over four warps along
+// K (the sums meet in shared memory): enough CTAs to fill the GPU at continuous-batching sizes and a four times shorter
+// loop per warp.  grid = (ceil(r / 2), ceil(m / 8)), block = 256.
 __global__ void __launch_bounds__(256) lora_down_rows8_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
                                                               float scale, int m, int k, int r, void *__restrict__ t, int bf16_out) {
+    __shared__ float part[8][8];  // [warp][row of x]
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row0 = blockIdx.y * 8, j = blockIdx.x * 8 + warp;
+    const int row0 = blockIdx.y * 8, j = blockIdx.x * 2 + (warp >> 2), kq = warp & 3;
     pdl_wait();  // x may be the previous kernel's output; t may still be read by it
-    if (j >= r) return;
-    const uint4 *ar = reinterpret_cast<const uint4 *>(a + static_cast<size_t>(j) * k);
     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int i = lane; i < k / 8; i += 32) {
-        const uint4 av = ar[i];
-        const uint32_t as[4] = {av.x, av.y, av.z, av.w};
+    if (j < r) {
+        const uint4 *ar = reinterpret_cast<const uint4 *>(a + static_cast<size_t>(j) * k);
+        const int pieces = k / 8, per = (pieces + 3) / 4;  // 16-byte pieces of a row, and of this warp's quarter of K
+        const int i1 = min(pieces, (kq + 1) * per);
+        for (int i = kq * per + lane; i < i1; i += 32) {
+            const uint4 av = ar[i];
+            const uint32_t as[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
-        for (int rr = 0; rr < 8; ++rr) {
-            const int row = row0 + rr < m ? row0 + rr : m - 1;  // (rows past m repeat the last one; their sums are dropped)
-            const uint4 xv = ld_cg_v4(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(row) * k) + i);
-            const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+            for (int rr = 0; rr < 8; ++rr) {
+                const int row = row0 + rr < m ? row0 + rr : m - 1;  // (rows past m repeat the last one; their sums are dropped)
+                const uint4 xv = ld_cg_v4(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(row) * k) + i);
+                const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                sum[rr] += __uint_as_float(xs[e] << 16) * __uint_as_float(as[e] << 16) +
-                           __uint_as_float(xs[e] & 0xFFFF0000u) * __uint_as_float(as[e] & 0xFFFF0000u);
+                for (int e = 0; e < 4; ++e)
+                    sum[rr] += __uint_as_float(xs[e] << 16) * __uint_as_float(as[e] << 16) +
+                               __uint_as_float(xs[e] & 0xFFFF0000u) * __uint_as_float(as[e] & 0xFFFF0000u);
+            }
         }
     }
 #pragma unroll
@@ -72,7 +78,13 @@ __global__ void __launch_bounds__(256) lora_down_rows8_kernel(const __nv_bfloat1
         float v = sum[rr];
 #pragma unroll
         for (int sh = 16; sh >= 1; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
-        if (lane == 0 && row0 + rr < m) store_t(t, static_cast<size_t>(row0 + rr) * r + j, v * scale, bf16_out);
+        if (lane == 0) part[warp][rr] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {  // the CTA's 2 x 8 results: the four K quarters are added in a fixed order
+        const int jj = threadIdx.x >> 3, rr = threadIdx.x & 7, jo = blockIdx.x * 2 + jj;
+        const float v = (part[4 * jj][rr] + part[4 * jj + 1][rr]) + (part[4 * jj + 2][rr] + part[4 * jj + 3][rr]);
+        if (jo < r && row0 + rr < m) store_t(t, static_cast<size_t>(row0 + rr) * r + jo, v * scale, bf16_out);
     }
 }
 
@@ -112,7 +124,7 @@ __global__ void __launch_bounds__(256) finish_kernel(const __nv_bfloat16 *__rest
 int launch_lora_down(const void *x, const void *lora_a, float scale, int m, int k, int r, void *t, int bf16_out, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     const bool rows8 = m > 32;
-    cfg.gridDim = rows8 ? dim3((r + 7) / 8, (m + 7) / 8, 1) : dim3((r + 7) / 8, m, 1);
+    cfg.gridDim = rows8 ? dim3((r + 1) / 2, (m + 7) / 8, 1) : dim3((r + 7) / 8, m, 1);
     cfg.blockDim = dim3(256);
     cfg.stream = stream;
     cudaLaunchAttribute attr;

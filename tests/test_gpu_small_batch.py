@@ -45,11 +45,11 @@ def _run(case, small_batch, m, n, device, groupsize=128):
 
 
 # one K stage, one tile; ragged row counts around the MMA's N steps of 16; K splits (q: 4, down: 6); many tiles per CTA;
-# the 128-row variant (65..128 rows: one accumulator buffer)
+# the 128-row variant (65..128 rows: one accumulator buffer), also with several tiles per CTA
 @pytest.mark.parametrize("m,k,n", [(1, 128, 256), (16, 256, 256), (17, 640, 512), (31, 2560, 4096), (33, 4096, 2560),
                                    (47, 9216, 2560), (48, 2560, 8192), (64, 2560, 18432), (64, 128, 256),
                                    (63, 1152, 38400), (65, 2560, 4096), (100, 9216, 2560),
-                                   (128, 2560, 18432), (127, 640, 512)])
+                                   (128, 2560, 18432), (127, 640, 512), (100, 640, 38400)])
 def test_small_batch_kernel_matches_the_oracle_and_the_general_kernel(cuda_device, m, k, n):
     case = _case(m, k, n, seed=3 * m + k + n, device=cuda_device)
     out = _run(case, True, m, n, cuda_device)

@@ -20,8 +20,9 @@
 // Roles (480 threads): warp 0 TMA producer, warps 1 and 14 MMA issuers (each issues four of the eight K=16 MMAs of a
 // stage into an accumulator of its own: one thread issues about one tcgen05.mma per 105 cycles), warps 2-5 epilogue,
 // warps 6-13 dequant in two teams of four warps (a team covers the four lane quarters) that take the stages in turn.
-// SwiGLU (gate and up columns interleaved in runs of 32, no K split): the warp that owns a run of up columns passes its sums
-// to the warp that owns the gate columns through shared memory, which writes silu(gate) * up.
+// The K loop is bound by the dequant instruction stream on the integer pipe (about 40 instructions per 16 K and lane).
+// SwiGLU (gate and up columns interleaved in runs of 32, no K split): the warp that owns a run of gate columns and the warp
+// that owns their up columns put their sums into shared memory and each writes silu(gate) * up for half of the rows.
 // LoRA delta (grouped scales): one extra stage at the start of a tile's K range, its tensor-memory operand the tile's rows of
 // lora_b and its activation tile t = scale * x * A^T (bf16, written by the kernel launched just before).
 // Every wait is bounded (w4a16_async.cuh); K splits write fp32 slabs that splitk_reduce_kernel sums.  Per-column scales
@@ -41,7 +42,7 @@ constexpr int kStages = 4;
 // drains one while the next fills), R = 128 one: 4 x 64 + 2 x 2 x 64 = 4 x 64 + 2 x 128 = 512 TMEM columns either way.
 constexpr int kWStageCols = kStageK / 2;         // TMEM columns of one stage of weights (two bf16 per cell)
 constexpr int kAccBase = kStages * kWStageCols;  // accumulators start at TMEM column 256
-constexpr int kTmemCols = 512;                   // 256 weights + 2 buffers x 2 issuers x 64 accumulator columns
+constexpr int kTmemCols = 512;                   // 256 of weights + 256 of accumulators
 constexpr int kDequantWarp0 = 6, kTeamWarps = 4, kTeams = 2;
 constexpr int kIssuerWarp2 = kDequantWarp0 + kTeamWarps * kTeams;
 constexpr int kThreads = (kIssuerWarp2 + 1) * 32;

@@ -67,7 +67,8 @@ kiln_w4a16_status_t kiln_w4a16_gemm_bf16(const void *A, const void *B, void *C, 
  * crates/kiln-model/src/forward.rs:2935-2939) and, for the gate+up projection, SiLU and the elementwise product
  * (forward.rs:2769-2839).
  *   lora_a    bf16 [lora_rank, k], lora_b bf16 [n, lora_rank] (device, 16-byte aligned), lora_rank a multiple of 8 up to
- *             128, lora_scale = alpha / rank.  The rank-r projection scale * x * A^T is computed first by a small kernel
+ *             128, lora_scale = alpha / rank.  lora_b is read like the packed weights, before the previous kernel in the
+ *             stream is known to have finished: it must not be the output of the kernel launched just before.  The rank-r projection scale * x * A^T is computed first by a small kernel
  *             into the workspace (fp32), the GEMM adds its product with B^T to the fp32 sums before rounding to bf16.
  *   swiglu    1: the packed matrix holds the gate and up projections as ONE matrix whose columns alternate in runs of
  *             32 (columns 64c .. 64c+31 are gate columns 32c .. 32c+31, columns 64c+32 .. 64c+63 the up columns of the
